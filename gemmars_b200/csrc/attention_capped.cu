@@ -7,8 +7,11 @@
 //                          dims of every q and k head (dim i pairs with i + rot/2; angle
 //                          float(pos) * inv_freq[i], float32) -> q rows, keys and values into pages
 //   gb_attention_capped:   score = (q . k) * scale; score <- cap * tanh(score / cap) when cap > 0;
-//                          keys lo..p with lo = max(0, p + 1 - window); softmax; output times
-//                          sigmoid(gate) * out_scale when a gate is given
+//                          keys lo..p with lo = max(0, p + 1 - window), and with `keep_first` the
+//                          keys 0..keep_first-1 as well, wherever the window stands; softmax, whose
+//                          denominator also holds exp(sink[head]) when sinks are given (a term
+//                          without key or value); output times sigmoid(gate) * out_scale when a
+//                          gate is given
 //
 // Cache layout as everywhere in the package: keys [pages, kv_heads, page_size, D], values
 // transposed inside a page [pages, kv_heads, Vd, page_size].
@@ -82,13 +85,14 @@ __global__ void __launch_bounds__(128) filter_rope_cache_kernel(
 }
 
 // taps: [(H + G) D + G Vd, K] float32 (K = 0: no filter); state: [slots, K - 1, channels] float32.
+// G = 0: the rows hold queries only (a layer that reads another layer's keys and values).
 GB_EXPORT int gb_filter_rope_cache(const void* u, int dtype, long long ldu, const float* taps, const float* state, int K,
                                    const float* inv_freq, int rot, const int* tok_pos, const int* tok_seq, const int* seq_slot,
                                    const int* cu, const int* page_table, int table_width, int page_size, void* q_out,
                                    long long ldq, void* kcache, void* vcache, int ntok, int H, int G, int D, int Vd,
                                    cudaStream_t stream) {
   if (ntok <= 0) return 0;
-  if (K < 0 || K > MAX_TAPS || rot < 0 || rot > D || rot % 2 || H <= 0 || G <= 0 || D <= 0 || D > MAX_HEAD || Vd <= 0)
+  if (K < 0 || K > MAX_TAPS || rot < 0 || rot > D || rot % 2 || H <= 0 || G < 0 || D <= 0 || D > MAX_HEAD || Vd <= 0)
     return GB_ERR_SIZE;
   if ((K > 0 && !taps) || (K > 1 && !state) || (rot > 0 && !inv_freq)) return GB_ERR_ARG;
   const dim3 grid(ntok, H + 2 * G);
@@ -105,13 +109,16 @@ GB_EXPORT int gb_filter_rope_cache(const void* u, int dtype, long long ldu, cons
   return gb_launch_status();
 }
 
-// One block per (token, query head); online softmax over chunks of 128 keys that start at lo.
+// One block per (token, query head); online softmax over chunks of 128 keys: first the kept keys
+// below the window (chunks from 0), then the window (chunks from lo).  A sink starts the running
+// maximum at its value and the running sum at one.
 template <typename T>
 __global__ void __launch_bounds__(CHUNK) attention_capped_kernel(
     const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride, const T* __restrict__ kcache,
     const T* __restrict__ vcache, const int* __restrict__ page_table, int table_width, int page_size, int G, int D, int Vd,
     const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ seq_slot, int H, int window,
-    float scale, float cap, const T* __restrict__ gate, long long gate_stride, float out_scale) {
+    int keep_first, const float* __restrict__ sink, float scale, float cap, const T* __restrict__ gate, long long gate_stride,
+    float out_scale) {
   extern __shared__ float smem[];
   pdl_release_next();
   pdl_wait_prior();
@@ -129,11 +136,15 @@ __global__ void __launch_bounds__(CHUNK) attention_capped_kernel(
   for (int i = tid; i < D; i += CHUNK) qs[i] = to_f32(qrow[i]);
   __syncthreads();
   const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
-  float m = -INFINITY, l = 0.f, acc[VPT] = {};
-  for (int c0 = lo; c0 < hi; c0 += CHUNK) {
+  float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f, acc[VPT] = {};
+  const int kept = min(keep_first, lo);          // kept keys that the window does not cover
+  const int kept_chunks = (kept + CHUNK - 1) / CHUNK;
+  for (int it = 0; it < kept_chunks || lo + (it - kept_chunks) * CHUNK < hi; ++it) {
+    const int c0 = it < kept_chunks ? it * CHUNK : lo + (it - kept_chunks) * CHUNK;
+    const int end = it < kept_chunks ? kept : hi;
     const int j = c0 + tid;
     float s = -INFINITY;
-    if (j < hi) {
+    if (j < end) {
       const int page = page_table[(size_t)slot * table_width + (j / page_size) % table_width];
       const int off = j % page_size;
       const T* kr = kcache + (((size_t)page * G + g) * page_size + off) * D;
@@ -144,12 +155,12 @@ __global__ void __launch_bounds__(CHUNK) attention_capped_kernel(
       if (cap > 0.f) s = cap * tanhf(s * inv_cap);
     }
     const float m_new = fmaxf(m, block_max(s, scratch));
-    const float pj = j < hi ? expf(s - m_new) : 0.f;
+    const float pj = j < end ? expf(s - m_new) : 0.f;
     p[tid] = pj;
     const float csum = block_sum(pj, scratch);   // also orders the writes of p and rows
     const float alpha = expf(m - m_new);
     l = l * alpha + csum;
-    const int n = min(CHUNK, hi - c0);
+    const int n = min(CHUNK, end - c0);
 #pragma unroll
     for (int u = 0; u < VPT; ++u) {
       const int d = tid + u * CHUNK;
@@ -177,20 +188,21 @@ __global__ void __launch_bounds__(CHUNK) attention_capped_kernel(
 GB_EXPORT int gb_attention_capped(const void* q, long long q_stride, void* out, long long out_stride, int dtype,
                                   const void* kcache, const void* vcache, const int* page_table, int table_width, int page_size,
                                   int G, int D, int Vd, const int* tok_pos, const int* tok_seq, const int* seq_slot, int ntok,
-                                  int H, int window, float scale, float cap, const void* gate, long long gate_stride,
-                                  float out_scale, cudaStream_t stream) {
+                                  int H, int window, int keep_first, const float* sink, float scale, float cap,
+                                  const void* gate, long long gate_stride, float out_scale, cudaStream_t stream) {
   if (ntok <= 0) return 0;
-  if (D <= 0 || Vd <= 0 || Vd > VPT * CHUNK || G <= 0 || H % G) return GB_ERR_SIZE;
+  if (D <= 0 || Vd <= 0 || Vd > VPT * CHUNK || G <= 0 || H % G || keep_first < 0) return GB_ERR_SIZE;
+  if (window <= 0) keep_first = 0;      // every key is seen already
   const size_t smem = (size_t)(D + CHUNK + 34) * sizeof(float) + CHUNK * sizeof(size_t) + 8;
   dim3 grid(ntok, H);
   if (dtype == GB_F32)
     gb_launch(attention_capped_kernel<float>, grid, CHUNK, smem, stream, (const float*)q, q_stride, (float*)out, out_stride,
               (const float*)kcache, (const float*)vcache, page_table, table_width, page_size, G, D, Vd, tok_pos, tok_seq,
-              seq_slot, H, window, scale, cap, (const float*)gate, gate_stride, out_scale);
+              seq_slot, H, window, keep_first, sink, scale, cap, (const float*)gate, gate_stride, out_scale);
   else if (dtype == GB_BF16)
     gb_launch(attention_capped_kernel<bf16>, grid, CHUNK, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
               (const bf16*)kcache, (const bf16*)vcache, page_table, table_width, page_size, G, D, Vd, tok_pos, tok_seq, seq_slot,
-              H, window, scale, cap, (const bf16*)gate, gate_stride, out_scale);
+              H, window, keep_first, sink, scale, cap, (const bf16*)gate, gate_stride, out_scale);
   else
     return GB_ERR_DTYPE;
   return gb_launch_status();

@@ -1,7 +1,9 @@
 // bfloat16 attention with capped scores on the tensor cores (mma.sync), for prompts, parts of
 // prompts and single positions alike: keys of GB_HEAD_DIM, values of GB_VALUE_DIM (compiled per
 // pair of sizes), score = (q . k) * scale, then cap * tanh(score / cap) when cap > 0, a window when
-// given, and the output times sigmoid(gate) * out_scale when a gate is given.
+// given (with `keep_first`, the keys 0..keep_first-1 are seen wherever the window stands), a sink
+// per head when given (exp(sink[head]) joins the softmax's denominator, with no key and no value),
+// and the output times sigmoid(gate) * out_scale when a gate is given.
 //
 // The arrangement is that of attention_prefill.cu: the 16 rows of an MMA are 16 consecutive
 // tokens of one sequence for one query head, each row masked at its own position and window;
@@ -43,7 +45,8 @@ __global__ void __launch_bounds__(MT * RH * 32)
 attention_capped_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                          const bf16* __restrict__ kcache, const bf16* __restrict__ vcache, PagedKV kv,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
-                         const int* __restrict__ seq_slot, int n_seqs, int nh, int window, int heads_per_cta, float scale,
+                         const int* __restrict__ seq_slot, int n_seqs, int nh, int window, int keep_first,
+                         const float* __restrict__ sink, int heads_per_cta, float scale,
                          float cap, const bf16* __restrict__ gate, long long gate_stride, float out_scale) {
   pdl_release_next();
   pdl_wait_prior();
@@ -101,8 +104,11 @@ attention_capped_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16
   for (int d = 0; d < VD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
   const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f, cap2 = cap * LOG2E, scale2 = scale * LOG2E;
-  for (int blk = lo_first / KEYS; blk * KEYS <= last; ++blk) {
-    const int key0 = blk * KEYS;
+  // blocks of 32 keys: first those of the kept keys that lie below the window's first block, then the window's
+  const int win_blk = lo_first / KEYS, kept_blks = min((keep_first + KEYS - 1) / KEYS, win_blk);
+  const int n_blks = kept_blks + last / KEYS - win_blk + 1;
+  for (int it = 0; it < n_blks; ++it) {
+    const int key0 = (it < kept_blks ? it : win_blk + it - kept_blks) * KEYS;
     const int page = kv.page_table[(size_t)slot * kv.table_width + (key0 / kv.page_size) % kv.table_width];
     const size_t page_base = ((size_t)page * kv.num_kv_heads + kvh) * kv.page_size * HD;
     const size_t value_base = ((size_t)page * kv.num_kv_heads + kvh) * kv.page_size * VD;
@@ -132,8 +138,8 @@ attention_capped_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16
         // in log2 units: cap * tanh(score * scale / cap) * log2(e), or score * scale * log2(e)
         const float a0 = cap > 0.f ? cap2 * tanh_fast(s[j][e] * scale * inv_cap) : s[j][e] * scale2;
         const float a1 = cap > 0.f ? cap2 * tanh_fast(s[j][2 + e] * scale * inv_cap) : s[j][2 + e] * scale2;
-        s[j][e] = (key >= lo0 && key <= pos0) ? a0 : -INFINITY;
-        s[j][2 + e] = (key >= lo1 && key <= pos1) ? a1 : -INFINITY;
+        s[j][e] = ((key >= lo0 || key < keep_first) && key <= pos0) ? a0 : -INFINITY;
+        s[j][2 + e] = ((key >= lo1 || key < keep_first) && key <= pos1) ? a1 : -INFINITY;
         mx0 = fmaxf(mx0, s[j][e]);
         mx1 = fmaxf(mx1, s[j][2 + e]);
       }
@@ -166,8 +172,16 @@ attention_capped_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16
   }
   l0 = quad_sum(l0);
   l1 = quad_sum(l1);
+  float keep0 = 1.f, keep1 = 1.f;       // what the sink leaves of the keys' share
+  if (sink) {
+    const float s2 = sink[head] * LOG2E, n0 = fmaxf(m0, s2), n1 = fmaxf(m1, s2);
+    keep0 = m0 == -INFINITY ? 0.f : exp2f(m0 - n0);
+    keep1 = m1 == -INFINITY ? 0.f : exp2f(m1 - n1);
+    l0 = l0 * keep0 + exp2f(s2 - n0);
+    l1 = l1 * keep1 + exp2f(s2 - n1);
+  }
   if (v0) {
-    const float inv = out_scale / l0;
+    const float inv = out_scale * keep0 / l0;
     bf16* dst = out + (size_t)(tok0 + g) * out_stride + (size_t)head * VD + 2 * c;
     const bf16* gt = gate ? gate + (size_t)(tok0 + g) * gate_stride + (size_t)head * VD + 2 * c : nullptr;
 #pragma unroll
@@ -182,7 +196,7 @@ attention_capped_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16
     }
   }
   if (v1) {
-    const float inv = out_scale / l1;
+    const float inv = out_scale * keep1 / l1;
     bf16* dst = out + (size_t)(tok0 + g + 8) * out_stride + (size_t)head * VD + 2 * c;
     const bf16* gt = gate ? gate + (size_t)(tok0 + g + 8) * gate_stride + (size_t)head * VD + 2 * c : nullptr;
 #pragma unroll
@@ -207,7 +221,8 @@ __global__ void __launch_bounds__(SPLIT * 32)
 attention_capped_single_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                          const bf16* __restrict__ kcache, const bf16* __restrict__ vcache, PagedKV kv,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
-                         const int* __restrict__ seq_slot, int n_seqs, int nh, int window, float scale,
+                         const int* __restrict__ seq_slot, int n_seqs, int nh, int window, int keep_first,
+                         const float* __restrict__ sink, float scale,
                          float cap, const bf16* __restrict__ gate, long long gate_stride, float out_scale) {
   pdl_release_next();
   pdl_wait_prior();
@@ -253,8 +268,10 @@ attention_capped_single_kernel(const bf16* __restrict__ q, long long q_stride, b
   for (int d = 0; d < VD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
   const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f, cap2 = cap * LOG2E, scale2 = scale * LOG2E;
-  for (int blk = lo_first / KEYS + warp; blk * KEYS <= last; blk += SPLIT) {
-    const int key0 = blk * KEYS;
+  const int win_blk = lo_first / KEYS, kept_blks = min((keep_first + KEYS - 1) / KEYS, win_blk);
+  const int n_blks = kept_blks + last / KEYS - win_blk + 1;
+  for (int it = warp; it < n_blks; it += SPLIT) {
+    const int key0 = (it < kept_blks ? it : win_blk + it - kept_blks) * KEYS;
     const int page = kv.page_table[(size_t)slot * kv.table_width + (key0 / kv.page_size) % kv.table_width];
     const size_t page_base = ((size_t)page * kv.num_kv_heads + kvh) * kv.page_size * HD;
     const size_t value_base = ((size_t)page * kv.num_kv_heads + kvh) * kv.page_size * VD;
@@ -284,8 +301,8 @@ attention_capped_single_kernel(const bf16* __restrict__ q, long long q_stride, b
         // in log2 units: cap * tanh(score * scale / cap) * log2(e), or score * scale * log2(e)
         const float a0 = cap > 0.f ? cap2 * tanh_fast(s[j][e] * scale * inv_cap) : s[j][e] * scale2;
         const float a1 = cap > 0.f ? cap2 * tanh_fast(s[j][2 + e] * scale * inv_cap) : s[j][2 + e] * scale2;
-        s[j][e] = (key >= lo0 && key <= pos0) ? a0 : -INFINITY;
-        s[j][2 + e] = (key >= lo1 && key <= pos1) ? a1 : -INFINITY;
+        s[j][e] = ((key >= lo0 || key < keep_first) && key <= pos0) ? a0 : -INFINITY;
+        s[j][2 + e] = ((key >= lo1 || key < keep_first) && key <= pos1) ? a1 : -INFINITY;
         mx0 = fmaxf(mx0, s[j][e]);
         mx1 = fmaxf(mx1, s[j][2 + e]);
       }
@@ -334,10 +351,11 @@ attention_capped_single_kernel(const bf16* __restrict__ q, long long q_stride, b
   __syncthreads();
   for (int idx = threadIdx.x; idx < rows * VD; idx += SPLIT * 32) {
     const int row = idx / VD, col = idx - row * VD;
-    float top = -INFINITY;
+    const float s2 = sink ? sink[head_base + row] * LOG2E : -INFINITY;
+    float top = s2;
 #pragma unroll
     for (int w = 0; w < SPLIT; ++w) top = fmaxf(top, pm[w * 16 + row]);
-    float total = 0.f, acc = 0.f;
+    float total = sink ? exp2f(s2 - top) : 0.f, acc = 0.f;
 #pragma unroll
     for (int w = 0; w < SPLIT; ++w) {
       const float m = pm[w * 16 + row];
@@ -360,10 +378,11 @@ attention_capped_single_kernel(const bf16* __restrict__ q, long long q_stride, b
 GB_EXPORT int gb_attention_capped_mma(const void* q, long long q_stride, void* out, long long out_stride,
                                       const void* kcache, const void* vcache, const int* page_table, int table_width,
                                       int page_size, int nkv, int hd, int vd, const int* cu_seqlens, const int* seq_start,
-                                      const int* seq_slot, int n_seqs, int ntok, int nh, int window, float scale, float cap,
-                                      const void* gate, long long gate_stride, float out_scale, int single, cudaStream_t stream) {
+                                      const int* seq_slot, int n_seqs, int ntok, int nh, int window, int keep_first,
+                                      const float* sink, float scale, float cap, const void* gate, long long gate_stride, float out_scale, int single, cudaStream_t stream) {
   if (ntok <= 0 || n_seqs <= 0) return 0;
-  if (hd != HD || vd != VD || nkv <= 0 || nh % nkv || page_size % KEYS) return GB_ERR_SIZE;
+  if (hd != HD || vd != VD || nkv <= 0 || nh % nkv || page_size % KEYS || keep_first < 0) return GB_ERR_SIZE;
+  if (window <= 0) keep_first = 0;      // every key is seen already
   if (((uintptr_t)q & 15) || (q_stride % 8) || ((uintptr_t)out & 3) || (out_stride % 2) || ((uintptr_t)kcache & 15) ||
       ((uintptr_t)vcache & 15) || ((uintptr_t)gate & 3) || (gate_stride % 2))
     return GB_ERR_SIZE;
@@ -384,7 +403,7 @@ GB_EXPORT int gb_attention_capped_mma(const void* q, long long q_stride, void* o
     if ((size_t)sgrid.x * sgrid.y > 2 * 148) {
       gb_launch(attention_capped_single_kernel, sgrid, SPLIT * 32, smem, stream,
           (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, kv, cu_seqlens,
-          seq_start, seq_slot, n_seqs, nh, window, scale, cap, (const bf16*)gate, gate_stride, out_scale);
+          seq_start, seq_slot, n_seqs, nh, window, keep_first, sink, scale, cap, (const bf16*)gate, gate_stride, out_scale);
     } else {
       // few CTAs: started only when the kernel before has ended, so that they spread one to an SM instead of
       // sharing the few SMs that had room while that kernel ran
@@ -395,13 +414,13 @@ GB_EXPORT int gb_attention_capped_mma(const void* q, long long q_stride, void* o
       cfg.stream = stream;
       cudaLaunchKernelEx(&cfg, attention_capped_single_kernel,
           (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, kv, cu_seqlens,
-          seq_start, seq_slot, n_seqs, nh, window, scale, cap, (const bf16*)gate, gate_stride, out_scale);
+          seq_start, seq_slot, n_seqs, nh, window, keep_first, sink, scale, cap, (const bf16*)gate, gate_stride, out_scale);
     }
     return gb_launch_status();
   }
   dim3 grid((ntok + TILE - 1) / TILE + n_seqs, nkv * chunks);
   gb_launch(attention_capped_mma_kernel, grid, MT * heads_per_cta * 32, 0, stream,
       (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, kv, cu_seqlens,
-      seq_start, seq_slot, n_seqs, nh, window, heads_per_cta, scale, cap, (const bf16*)gate, gate_stride, out_scale);
+      seq_start, seq_slot, n_seqs, nh, window, keep_first, sink, heads_per_cta, scale, cap, (const bf16*)gate, gate_stride, out_scale);
   return gb_launch_status();
 }

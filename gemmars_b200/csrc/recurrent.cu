@@ -520,3 +520,209 @@ GB_EXPORT int gb_gated_group_norm(const float* y, const float* gate, long long l
     return GB_ERR_DTYPE;
   return gb_launch_status();
 }
+
+// ------------------------------------------------------------------ mixes with the token before
+// out[s, t, c] = x[t, c] + (x[t - 1, c] - x[t, c]) * mu[s, c] for each of the n_mix rows of mu: every
+// consumer reads its own blend of a token's row and the row before it in the same sequence.  The
+// row before a step's first row of a sequence is the state's (float32 [slots, C], zeros for a new
+// sequence); afterwards the state holds the step's last row of the sequence.  In a step of single
+// tokens (`single`) the thread that read the state writes it; otherwise shift_state_kernel follows.
+template <typename T>
+__global__ void __launch_bounds__(256) shift_mix_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ mu,
+                                                       float* __restrict__ state, const int* __restrict__ cu,
+                                                       const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                                                       T* __restrict__ out, int ntok, int C, int n_mix, int single) {
+  pdl_release_next();
+  pdl_wait_prior();
+  const int t = blockIdx.x, b = tok_seq[t];
+  const bool first = t == cu[b];
+  float* st = state + (size_t)seq_slot[b] * C;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    const float cur = to_f32(x[(size_t)t * ldx + c]);
+    const float before = first ? st[c] : to_f32(x[(size_t)(t - 1) * ldx + c]);
+    const float d = before - cur;
+    for (int s = 0; s < n_mix; ++s) out[((size_t)s * ntok + t) * C + c] = from_f32<T>(fmaf(d, mu[(size_t)s * C + c], cur));
+    if (single) st[c] = cur;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) shift_state_kernel(const T* __restrict__ x, long long ldx, float* __restrict__ state,
+                                                         const int* __restrict__ cu, const int* __restrict__ seq_slot, int C) {
+  pdl_release_next();
+  pdl_wait_prior();
+  const int b = blockIdx.x, last = cu[b + 1] - 1;
+  if (last < cu[b]) return;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x)
+    state[(size_t)seq_slot[b] * C + c] = to_f32(x[(size_t)last * ldx + c]);
+}
+
+// mu: [n_mix, C] float32; out: [n_mix, ntok, C] in x's type; state: [slots, C] float32.
+GB_EXPORT int gb_shift_mix(const void* x, int dtype, long long ldx, const float* mu, float* state, const int* cu,
+                           const int* tok_seq, const int* seq_slot, void* out, int ntok, int nseq, int C, int n_mix,
+                           cudaStream_t stream) {
+  if (ntok <= 0) return 0;
+  if (C <= 0 || n_mix <= 0 || nseq <= 0) return GB_ERR_SIZE;
+  const int single = ntok == nseq;
+  const dim3 grid(ntok, (C + 1023) / 1024), sgrid(nseq, (C + 1023) / 1024);
+  if (dtype == GB_F32) {
+    gb_launch(shift_mix_kernel<float>, grid, 256, 0, stream, (const float*)x, ldx, mu, state, cu, tok_seq, seq_slot, (float*)out,
+              ntok, C, n_mix, single);
+    if (!single) gb_launch(shift_state_kernel<float>, sgrid, 256, 0, stream, (const float*)x, ldx, state, cu, seq_slot, C);
+  } else if (dtype == GB_BF16) {
+    gb_launch(shift_mix_kernel<bf16>, grid, 256, 0, stream, (const bf16*)x, ldx, mu, state, cu, tok_seq, seq_slot, (bf16*)out,
+              ntok, C, n_mix, single);
+    if (!single) gb_launch(shift_state_kernel<bf16>, sgrid, 256, 0, stream, (const bf16*)x, ldx, state, cu, seq_slot, C);
+  } else {
+    return GB_ERR_DTYPE;
+  }
+  return gb_launch_status();
+}
+
+// ------------------------------------------------------------------ decay from a low-rank projection
+// w[t, c] = exp(-exp(base[c] + sum_j W[c, j] tanh(z[t, j]))): the second half of a two-matrix decay
+// whose first product z = W1 x is made by the framework's product in float32.  tanh, the sum, both
+// exponentials and the result are float32; the rank is small (tens), so a thread takes a channel.
+template <typename T>
+__global__ void __launch_bounds__(128) lowrank_decay_kernel(const float* __restrict__ z, int rank, const T* __restrict__ W,
+                                                           const float* __restrict__ base, float* __restrict__ w, int C) {
+  extern __shared__ float th[];      // tanh(z[t, :])
+  pdl_release_next();
+  pdl_wait_prior();
+  const int t = blockIdx.x;
+  for (int j = threadIdx.x; j < rank; j += blockDim.x) th[j] = tanhf(z[(size_t)t * rank + j]);
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < rank; ++j) acc = fmaf(to_f32(W[(size_t)c * rank + j]), th[j], acc);
+    w[(size_t)t * C + c] = expf(-expf(acc + base[c]));
+  }
+}
+
+// z: [ntok, rank] float32; W: [C, rank] float32 or bfloat16; base: [C]; w: [ntok, C] float32.
+GB_EXPORT int gb_lowrank_decay(const float* z, int rank, const void* W, int w_dtype, const float* base, float* w, int ntok,
+                               int C, cudaStream_t stream) {
+  if (ntok <= 0) return 0;
+  if (rank <= 0 || rank > 8192 || C <= 0) return GB_ERR_SIZE;
+  if (w_dtype == GB_F32)
+    gb_launch(lowrank_decay_kernel<float>, dim3(ntok), 128, rank * sizeof(float), stream, z, rank, (const float*)W, base, w, C);
+  else if (w_dtype == GB_BF16)
+    gb_launch(lowrank_decay_kernel<bf16>, dim3(ntok), 128, rank * sizeof(float), stream, z, rank, (const bf16*)W, base, w, C);
+  else
+    return GB_ERR_DTYPE;
+  return gb_launch_status();
+}
+
+// ------------------------------------------------------------------ linear attention with a decay per key channel
+// The state of a head is S [dim, vdim]; blocks, columns, lanes and the order in memory as for the
+// delta rule (dim <= 32 P).  Per token, with w the decay of every key channel (0..1) and u a
+// bonus per head and key channel that only the token itself gets:
+//   y = (S + diag(u) k v^T)^T r = S^T r + (sum_d r_d u_d k_d) v;   S <- diag(w) S + k v^T
+// The read-out sees the state as the tokens before left it.  Tokens come in groups of GR by
+// asynchronous copies, a group ahead; the sum over r u k is taken for the group at once, a token
+// a warp.  Everything is float32.
+template <int P, int GR>
+__global__ void __launch_bounds__(32 * P) wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
+                                                         const float* __restrict__ w, long long ld, const float* __restrict__ v,
+                                                         long long ldv, const float* __restrict__ bonus, float* __restrict__ state,
+                                                         const int* __restrict__ cu, const int* __restrict__ seq_slot,
+                                                         float* __restrict__ y, int H, int D, int V) {
+  constexpr int DP = P * SLICE;
+  __shared__ __align__(16) float rkw[2][GR][3][padded_size(P)];   // [buffer][token][r | k | w][dims, padded]
+  __shared__ float vs[2][GR][32];
+  __shared__ float us[padded_size(P)];
+  __shared__ float ruk[GR];
+  pdl_wait_prior();
+  const int b = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+  const int col = blockIdx.z * 32 + tid / P, part = tid % P, lane = tid & 31, warp = tid >> 5;
+  const bool live = col < V;
+  const int t0 = cu[b], t1 = cu[b + 1];
+  float4* Sg = (float4*)(state + ((size_t)seq_slot[b] * H + head) * 8 * V * P * 4);
+  float S[SLICE];
+#pragma unroll
+  for (int q = 0; q < SLICE / 4; ++q) {
+    const float4 s4 = live ? Sg[((size_t)q * V + col) * P + part] : make_float4(0.f, 0.f, 0.f, 0.f);
+    S[4 * q] = s4.x; S[4 * q + 1] = s4.y; S[4 * q + 2] = s4.z; S[4 * q + 3] = s4.w;
+  }
+  us[padded(tid)] = tid < D ? bonus[(size_t)head * D + tid] : 0.f;
+  if (tid >= D)      // the dims beyond the head's are zeros, written once
+    for (int j = 0; j < 2 * GR; ++j)
+      rkw[j / GR][j % GR][0][padded(tid)] = rkw[j / GR][j % GR][1][padded(tid)] = rkw[j / GR][j % GR][2][padded(tid)] = 0.f;
+  auto bring = [&](int first, int buf) {
+    for (int j = 0; j < GR && first + j < t1; ++j) {
+      const size_t t = first + j;
+      if (tid < D) {
+        copy_async4(&rkw[buf][j][0][padded(tid)], r + t * ld + head * D + tid);
+        copy_async4(&rkw[buf][j][1][padded(tid)], k + t * ld + head * D + tid);
+        copy_async4(&rkw[buf][j][2][padded(tid)], w + t * ld + head * D + tid);
+      }
+      if (live && part == 0) copy_async4(&vs[buf][j][tid / P], v + t * ldv + head * V + col);
+    }
+    copy_async_commit();
+  };
+  bring(t0, 0);
+  for (int first = t0; first < t1; first += GR) {
+    const int buf = ((first - t0) / GR) & 1;
+    if (first + GR < t1) {
+      bring(first + GR, buf ^ 1);
+      copy_async_wait<1>();
+    } else {
+      copy_async_wait<0>();
+    }
+    __syncthreads();
+    const int n = min(GR, t1 - first);
+    for (int j = warp; j < n; j += P) {       // a token a warp: what the state has no part in
+      float s = 0.f;
+      for (int i = lane; i < DP; i += 32) s = fmaf(rkw[buf][j][0][padded(i)] * us[padded(i)], rkw[buf][j][1][padded(i)], s);
+      s = warp_sum(s);
+      if (lane == 0) ruk[j] = s;
+    }
+    __syncthreads();
+    for (int j = 0; j < n; ++j) {
+      const float4* rs = (const float4*)(rkw[buf][j][0] + part * (SLICE + 4));
+      const float4* ks = (const float4*)(rkw[buf][j][1] + part * (SLICE + 4));
+      const float4* ws = (const float4*)(rkw[buf][j][2] + part * (SLICE + 4));
+      const float vc = live ? vs[buf][j][tid / P] : 0.f;
+      float sr = 0.f, sr2 = 0.f;
+#pragma unroll
+      for (int q = 0; q < SLICE / 4; ++q) {
+        const float4 rv = rs[q], kv = ks[q], wv = ws[q];
+        sr = fmaf(S[4 * q], rv.x, sr); sr2 = fmaf(S[4 * q + 1], rv.y, sr2);
+        sr = fmaf(S[4 * q + 2], rv.z, sr); sr2 = fmaf(S[4 * q + 3], rv.w, sr2);
+        S[4 * q] = fmaf(wv.x, S[4 * q], kv.x * vc);
+        S[4 * q + 1] = fmaf(wv.y, S[4 * q + 1], kv.y * vc);
+        S[4 * q + 2] = fmaf(wv.z, S[4 * q + 2], kv.z * vc);
+        S[4 * q + 3] = fmaf(wv.w, S[4 * q + 3], kv.w * vc);
+      }
+      sr = lanes_sum<P>(sr + sr2);
+      if (live && part == 0) y[(size_t)(first + j) * H * V + head * V + col] = fmaf(ruk[j], vc, sr);
+    }
+    __syncthreads();   // the group after next is brought into this buffer; ruk is written again
+  }
+  pdl_release_next();
+  if (live) {
+#pragma unroll
+    for (int q = 0; q < SLICE / 4; ++q)
+      Sg[((size_t)q * V + col) * P + part] = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
+  }
+}
+
+// r, k, w: rows of ld floats, head h at h * D; v: rows of ldv floats, head h at h * V; bonus: [H, D];
+// state: [slots, H, gb_state_floats(D, V)] float32; y: [ntok, H * V].
+GB_EXPORT int gb_wkv_scan(const float* r, const float* k, const float* w, long long ld, const float* v, long long ldv,
+                          const float* bonus, float* state, const int* cu, const int* seq_slot, float* y, int nseq, int H, int D,
+                          int V, cudaStream_t stream) {
+  if (nseq <= 0) return 0;
+  if (H <= 0 || V <= 0 || D <= 0 || D > 8 * SLICE || ((uintptr_t)state & 15)) return GB_ERR_SIZE;
+  dim3 grid(nseq, H, (V + 31) / 32);
+#define GB_WKV(P, GR) \
+  launch_scan(wkv_scan_kernel<P, GR>, grid, 32 * P, stream, r, k, w, ld, v, ldv, bonus, state, cu, seq_slot, y, H, D, V)
+  switch (lanes_for(D)) {
+    case 1: GB_WKV(1, 8); break;
+    case 2: GB_WKV(2, 8); break;
+    case 4: GB_WKV(4, 8); break;
+    default: GB_WKV(8, 4);
+  }
+#undef GB_WKV
+  return gb_launch_status();
+}

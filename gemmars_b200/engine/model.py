@@ -181,11 +181,12 @@ def build_model(folder: Optional[str] = None, *, raw_config: Optional[dict] = No
     if folder is not None:
         arch, cfg = load_config(folder)
         files = ModelFiles(folder)
-        names = files.names()
+        # {name: shape}: a plan builder may look a name up, or read a size that only a shape gives
+        names = {n: tuple(files.info(n)[1]) for n in files.names()}
     else:
         arch = resolve_architecture(raw_config)
         cfg = arch.config_class.from_dict(raw_config)
-        files, names = None, set(tensors)
+        files, names = None, {n: tuple(t.shape) for n, t in tensors.items()}
     plan = arch.build_plan(cfg, names)
     model = DecoderModel(plan, dtype, device)
     model.config = cfg

@@ -1530,6 +1530,63 @@ def gated_group_norm(y, gate, weight, out, group_size: int, eps: float, gate_fir
            _nbytes(y, out) + y.numel() * 4)
 
 
+def shift_mix(x, mu, state, cu_seqlens, tok_seq, seq_slot):
+    """[n_mix, T, C] in x's type: out[s, t] = x[t] + (x[t - 1] - x[t]) * mu[s] along each sequence of
+    the packed step, in float32 before the rounding.  The row before a sequence's first row of
+    the step is ``state`` [slots + 1, C] (float32; zeros for a new sequence), which then takes the
+    sequence's last row."""
+    _cuda(x, mu, state, cu_seqlens, tok_seq, seq_slot)
+    n_mix, c = mu.shape
+    assert mu.dtype == torch.float32 and mu.is_contiguous() and x.shape[1] == c
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (c,)
+    xp, ldx = _cols(x)
+    out = torch.empty((n_mix, x.shape[0], c), dtype=x.dtype, device=x.device)
+    f = _fn("recurrent", "gb_shift_mix", [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(xp, dtype_code(x.dtype), ldx, mu.data_ptr(), state.data_ptr(), cu_seqlens.data_ptr(), tok_seq.data_ptr(),
+             seq_slot.data_ptr(), out.data_ptr(), x.shape[0], seq_slot.numel(), c, n_mix, _stream()), "shift_mix",
+           "elementwise", _nbytes(x, out))
+    if x.shape[0] != seq_slot.numel():
+        count_launches(1)      # the kernel that keeps each sequence's last row
+    return out
+
+
+def lowrank_decay(z, w2, base):
+    """float32 [T, C]: exp(-exp(base + tanh(z) @ w2.T)), all of it float32 arithmetic.  ``z``: float32
+    [T, rank]; ``w2``: [C, rank] float32 or bfloat16; ``base``: float32 [C]."""
+    _cuda(z, w2, base)
+    c, rank = w2.shape
+    assert z.dtype == torch.float32 and z.is_contiguous() and z.shape[1] == rank and w2.is_contiguous()
+    assert base.dtype == torch.float32 and base.numel() == c
+    out = torch.empty((z.shape[0], c), dtype=torch.float32, device=z.device)
+    f = _fn("recurrent", "gb_lowrank_decay", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(z.data_ptr(), rank, w2.data_ptr(), dtype_code(w2.dtype), base.data_ptr(), out.data_ptr(), z.shape[0], c,
+             _stream()), "lowrank_decay", "elementwise", _nbytes(z, out, w2))
+    return out
+
+
+def wkv_scan(r, k, w, v, bonus, state, cu_seqlens, seq_slot, y, heads, dim, vdim):
+    """Linear attention with a decay per key channel over each sequence of the packed step (float32):
+    y = S^T r + (sum_d r_d bonus_d k_d) v, then S <- diag(w) S + k v^T, per head.  r, k, w: [T, heads *
+    dim] with equal row strides; v: [T, heads * vdim]; ``bonus`` [heads, dim]; ``state`` [slots + 1,
+    heads, recurrent_state_floats(dim, vdim)] (see recurrent_state_matrix); dim up to 256."""
+    _cuda(r, k, w, v, bonus, state, cu_seqlens, seq_slot, y)
+    for t in (r, k, w, v, bonus, state, y):
+        assert t.dtype == torch.float32
+    rp, ld = _cols(r)
+    kp, ldk = _cols(k)
+    wp, ldw = _cols(w)
+    vp, ldv = _cols(v)
+    assert ld == ldk == ldw and y.is_contiguous() and y.shape[1] == heads * vdim and bonus.is_contiguous()
+    assert bonus.numel() == heads * dim
+    assert state.is_contiguous() and tuple(state.shape[1:]) == (heads, recurrent_state_floats(dim, vdim))
+    f = _fn("recurrent", "gb_wkv_scan", [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(rp, kp, wp, ld, vp, ldv, bonus.data_ptr(), state.data_ptr(), cu_seqlens.data_ptr(), seq_slot.data_ptr(),
+             y.data_ptr(), seq_slot.numel(), heads, dim, vdim, _stream()), "wkv_scan", "attention",
+           _nbytes(y) * 5 + 2 * seq_slot.numel() * heads * dim * vdim * 4)
+
+
 # --------------------------------------------------------------------------- attention with capped scores
 
 def filter_rope_cache(u, taps, state, inv_freq, rot, ctx_pos, tok_seq, seq_slot, cu_seqlens, page_table, page_size, q_out,
@@ -1578,14 +1635,18 @@ def attention_capped_units(compute: str, dim: int, vdim: int, page_size: int = 6
 
 
 def attention_capped(ctx, q, out, heads, kcache, vcache, page_table, page_size, window, scale, cap, gate=None,
-                     out_scale: float = 1.0):
+                     out_scale: float = 1.0, keep_first: int = 0, sink=None):
     """Attention of the step's queries [T, heads * dim] over the cache with keys of ``dim`` and
     values of ``vdim``: score = (q . k) * scale, capped as cap * tanh(score / cap) when ``cap``;
-    a window of ``window`` keys when given; the output times sigmoid(gate) * out_scale.  bfloat16
+    a window of ``window`` keys when given, beside which the first ``keep_first`` keys of the
+    sequence stay visible; ``sink`` (float32 [heads]): exp(sink[head]) is one more term of the
+    softmax's denominator; the output times sigmoid(gate) * out_scale.  bfloat16
     steps run on the tensor cores where the sizes allow (keys a multiple of 16, values of 8, up to
     256), prompts and single tokens alike; float32 and other sizes run the plain kernel."""
-    _cuda(q, out, kcache, vcache, page_table, gate)
+    _cuda(q, out, kcache, vcache, page_table, gate, sink)
     groups, dim, vdim = kcache.shape[1], kcache.shape[3], vcache.shape[2]
+    assert sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == heads)
+    keep_first = int(keep_first or 0)
     qp, ldq = _cols(q)
     op, ldo = _cols(out)
     gp, ldg = _cols(gate) if gate is not None else (None, 0)
@@ -1596,18 +1657,19 @@ def attention_capped(ctx, q, out, heads, kcache, vcache, page_table, page_size, 
             and ldo % 2 == 0 and (gp or 0) % 4 == 0 and ldg % 2 == 0):
         f = _fn("attention_capped_mma", "gb_attention_capped_mma",
                 [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_longlong, c_float,
-                 c_int, c_void_p], (("GB_HEAD_DIM", dim), ("GB_VALUE_DIM", vdim)))
+                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_float, c_void_p,
+                 c_longlong, c_float, c_int, c_void_p], (("GB_HEAD_DIM", dim), ("GB_VALUE_DIM", vdim)))
         _check(f(qp, ldq, op, ldo, kcache.data_ptr(), vcache.data_ptr(), page_table.data_ptr(), page_table.shape[1], page_size,
                  groups, dim, vdim, ctx.cu_seqlens.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_slot.data_ptr(), ctx.n_seqs,
-                 q.shape[0], heads, int(window or 0), scale, float(cap or 0.0), gp, ldg, out_scale,
+                 q.shape[0], heads, int(window or 0), keep_first, _ptr(sink), scale, float(cap or 0.0), gp, ldg, out_scale,
                  1 if q.shape[0] == ctx.n_seqs else 0, _stream()),
                "attention_capped_mma", "attention", 2 * q.numel() * q.element_size())
         return
     f = _fn("attention_capped", "gb_attention_capped",
             [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_longlong, c_float, c_void_p])
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_float, c_void_p, c_longlong, c_float,
+             c_void_p])
     _check(f(qp, ldq, op, ldo, dtype_code(q.dtype), kcache.data_ptr(), vcache.data_ptr(), page_table.data_ptr(),
              page_table.shape[1], page_size, groups, dim, vdim, ctx.tok_pos.data_ptr(), ctx.tok_seq.data_ptr(),
-             ctx.seq_slot.data_ptr(), q.shape[0], heads, int(window or 0), scale, float(cap or 0.0), gp, ldg, out_scale,
-             _stream()), "attention_capped", "attention", 2 * q.numel() * q.element_size())
+             ctx.seq_slot.data_ptr(), q.shape[0], heads, int(window or 0), keep_first, _ptr(sink), scale, float(cap or 0.0),
+             gp, ldg, out_scale, _stream()), "attention_capped", "attention", 2 * q.numel() * q.element_size())

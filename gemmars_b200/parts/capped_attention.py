@@ -6,14 +6,22 @@ For one token, with h the mixer's input:
   each channel passes a causal filter over time (``conv`` taps, no bias, no activation; 0: none);
   the position encoding turns q and k (a ``rotary`` part with the "half" layout, or None);
   score = (q . k) * scale, then cap * tanh(score / cap) when ``softcap``; a query sees itself and
-  the ``window`` - 1 positions before it (None: all); ordinary softmax; the heads side by side are
-  multiplied by sigmoid(W_g h) when ``gate``, then W_o, added into the residual.
+  the ``window`` - 1 positions before it (None: all), and with ``keep_first`` the sequence's first
+  ``keep_first`` positions as well, at their true places, however far the window has moved on;
+  softmax, whose denominator with ``sink`` also holds exp(s_head), a learned number per head that
+  has no key and no value; the heads side by side are multiplied by sigmoid(W_g h) when ``gate``,
+  then W_o, added into the residual.
 
 Keys (filtered and rotated) and values (filtered) live in the paged cache that every attention
 of the package uses (a window's pages are a ring); the filter's last ``conv`` - 1 inputs are a
 state per sequence.  Scores, softmax, angles and the gate are float32.  bfloat16 steps run on
-the tensor cores where the head sizes allow (kernels.attention_capped).  Parameters: hidden_size,
-heads, kv_heads, dim, vdim, bias, conv, window, scale, softcap, gate, position, out_scale.
+the tensor cores where the head sizes allow (kernels.attention_capped).  A part with ``has_kv``
+False has no k and v matrices: it runs its own queries, mask and sink over the keys and values of
+the schedule entry whose cache it is given.  A window's pages are a ring only with ``ring`` (the
+default) and no kept first positions; otherwise every page stays and the window is the kernels'
+mask alone, which is what a layer needs whose cache another layer with another mask reads.
+Parameters: hidden_size, heads, kv_heads, dim, vdim, bias, conv, window, keep_first, sink, scale,
+softcap, gate, position, has_kv, ring, out_scale.
 """
 from __future__ import annotations
 
@@ -38,6 +46,10 @@ class CappedAttention(Part):
         self.bias, self.gate = bool(p.get("bias", False)), bool(p.get("gate", False))
         self.taps = int(p.get("conv") or 0)
         self.window = p.get("window")
+        self.keep_first = int(p.get("keep_first") or 0)
+        self.sink = bool(p.get("sink", False))
+        self.has_kv = bool(p.get("has_kv", True))
+        self.ring = bool(p.get("ring", True)) and self.keep_first == 0
         self.scale = float(p["scale"]) if p.get("scale") is not None else float(self.dim) ** -0.5
         self.softcap = float(p.get("softcap") or 0.0)
         self.out_scale = float(p.get("out_scale", 1.0))
@@ -49,46 +61,62 @@ class CappedAttention(Part):
             raise ValueError(f"capped_attention: values of {self.vdim} are wider than the kernel takes (512)")
         if not 0 <= self.taps <= 8:
             raise ValueError(f"capped_attention: a filter of {self.taps} taps is not supported (0 to 8)")
+        if self.taps > 1 and not self.has_kv:
+            raise ValueError("capped_attention: a part without keys and values of its own cannot keep a filter's memory")
+        if self.keep_first < 0:
+            raise ValueError(f"capped_attention: keep_first must not be negative, got {self.keep_first}")
         pos = p.get("position")
         self.position = build_part("position", pos, compute) if pos is not None else None
         if self.position is not None and not (isinstance(self.position, Rotary) and self.position.layout == "half"):
             raise ValueError("capped_attention: the position encoding must be a rotary part with the half layout")
-        self.channels = (self.heads + self.kv_heads) * self.dim + self.kv_heads * self.vdim     # q | k | v
-        self.proj = self.o = self.filter = None
+        self.own_kv = self.kv_heads if self.has_kv else 0
+        self.channels = (self.heads + self.own_kv) * self.dim + self.own_kv * self.vdim     # q | k | v
+        self.proj = self.o = self.filter = self.sinks = None
 
     def wants(self):
         h, nh, nkv, d, vd = self.hidden_size, self.heads, self.kv_heads, self.dim, self.vdim
-        w = {"q": TensorWant((nh * d, h)), "k": TensorWant((nkv * d, h)), "v": TensorWant((nkv * vd, h)),
-             "o": TensorWant((h, nh * vd))}
+        w = {"q": TensorWant((nh * d, h)), "o": TensorWant((h, nh * vd))}
+        if self.has_kv:
+            w.update({"k": TensorWant((nkv * d, h)), "v": TensorWant((nkv * vd, h))})
         if self.bias:
-            w.update({"q_bias": TensorWant((nh * d,), "vector"), "k_bias": TensorWant((nkv * d,), "vector"),
-                      "v_bias": TensorWant((nkv * vd,), "vector")})
+            w["q_bias"] = TensorWant((nh * d,), "vector")
+            if self.has_kv:
+                w.update({"k_bias": TensorWant((nkv * d,), "vector"), "v_bias": TensorWant((nkv * vd,), "vector")})
         if self.taps:
-            w.update({"q_conv": TensorWant((nh * d, self.taps), "vector"), "k_conv": TensorWant((nkv * d, self.taps), "vector"),
-                      "v_conv": TensorWant((nkv * vd, self.taps), "vector")})
+            w["q_conv"] = TensorWant((nh * d, self.taps), "vector")
+            if self.has_kv:
+                w.update({"k_conv": TensorWant((nkv * d, self.taps), "vector"),
+                          "v_conv": TensorWant((nkv * vd, self.taps), "vector")})
         if self.gate:
             w["g"] = TensorWant((nh * vd, h))
+        if self.sink:
+            w["sink"] = TensorWant((nh,), "vector")
         return w
 
     def load(self, t):
-        names = ["q", "k", "v"] + (["g"] if self.gate else [])
+        qkv = ["q", "k", "v"] if self.has_kv else ["q"]
+        names = qkv + (["g"] if self.gate else [])
         bias = None
         if self.bias:
-            parts = [t["q_bias"], t["k_bias"], t["v_bias"]]
+            parts = [t[n + "_bias"] for n in qkv]
             if self.gate:
                 parts.append(torch.zeros(self.heads * self.vdim, dtype=torch.float32, device=t["q_bias"].device))
             bias = torch.cat(parts)
         self.proj = Linear(torch.cat([t[n] for n in names], dim=0), bias)     # one product: [q | k | v | gate]
         self.o = Linear(t["o"])
         if self.taps:
-            self.filter = torch.cat([t["q_conv"], t["k_conv"], t["v_conv"]], dim=0).contiguous()
+            self.filter = torch.cat([t[n + "_conv"] for n in qkv], dim=0).contiguous()
+        if self.sink:
+            self.sinks = t["sink"].to(torch.float32).contiguous()
 
     def kernel_units(self):
         return (kernels.gemm_units(self.compute) + kernels.attention_capped_units(self.compute, self.dim, self.vdim)
                 + ([("recurrent", ())] if self.taps > 1 else []))
 
     def cache_needs(self):
-        needs = [KVNeed(self.kv_heads, self.dim, self.window, self.vdim)]
+        if not self.has_kv:
+            return []
+        needs = [KVNeed(self.kv_heads, self.dim, self.window if self.ring else None, self.vdim)]
         if self.taps > 1:
             needs.append(StateNeed((self.taps - 1, self.channels)))
         return needs
@@ -97,9 +125,16 @@ class CappedAttention(Part):
         return self.proj.bytes() + self.o.bytes() + (4 * self.filter.numel() if self.filter is not None else 0)
 
     def forward(self, ctx, h, residual, caches, writes_cache=True):
-        if not writes_cache:
-            raise ValueError("capped_attention: running on another layer's keys and values is not supported")
+        if writes_cache != self.has_kv:
+            raise ValueError("capped_attention: a part with keys and values of its own writes its own cache, and one "
+                             "without reads another entry's (has_kv and the schedule's cache_of must agree)")
         group, kc, vc = caches[0]
+        if tuple(kc.shape[1:]) != (self.kv_heads, group.page_size, self.dim) or vc.shape[2] != self.vdim:
+            raise ValueError(f"capped_attention: the cache holds keys {tuple(kc.shape[1:])} and values of {vc.shape[2]}, "
+                             f"this part reads {self.kv_heads} heads of {self.dim} and {self.vdim}")
+        if group.need.window is not None and (self.keep_first or self.window is None or self.window > group.need.window):
+            raise ValueError("capped_attention: the cache keeps a ring of the last positions only, which does not hold "
+                             "what this part's mask sees")
         filter_state = caches[1] if self.taps > 1 else None
         nh, d, vd, c = self.heads, self.dim, self.vdim, self.channels
         p = self.proj(h)
@@ -108,12 +143,12 @@ class CappedAttention(Part):
         q = torch.empty((t, nh * d), dtype=p.dtype, device=p.device)
         kernels.filter_rope_cache(p[:, :c], self.filter, filter_state, self.position.inv_freq(p.device) if rot else None, rot,
                                   ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, ctx.cu_seqlens, group.page_table, group.page_size,
-                                  q, kc, vc, nh, self.kv_heads, d, vd)
+                                  q, kc if self.has_kv else None, vc if self.has_kv else None, nh, self.own_kv, d, vd)
         if self.taps > 1:
             kernels.short_filter_state(p[:, :c], filter_state, ctx.cu_seqlens, ctx.seq_slot, self.taps)
         att = torch.empty((t, nh * vd), dtype=p.dtype, device=p.device)
         kernels.attention_capped(ctx, q, att, nh, kc, vc, group.page_table, group.page_size, self.window, self.scale,
-                                 self.softcap, p[:, c:] if self.gate else None, self.out_scale)
+                                 self.softcap, p[:, c:] if self.gate else None, self.out_scale, self.keep_first, self.sinks)
         self.o.add_into(att, residual)
 
 

@@ -10,7 +10,8 @@ The experts' matrices are stacked at load ([experts, 2 ff, hidden]: gate rows th
 [experts, hidden, ff]) so that a kernel finds an expert by its index alone.  Parameters:
 hidden_size, experts, top, ff, limit, alpha (1.702), shift (1.0), router_bias, and ``shared``
 (None, or {"ff", "limit", "gate"}: its width, its clamp, and whether its output is multiplied by
-a sigmoid of one number per token).
+a sigmoid of one number per token).  A ``limit`` of None clamps nothing; with alpha 1 and shift 0
+the expert is then the plain gated form silu(gate h) * (up h).
 """
 from __future__ import annotations
 
@@ -31,13 +32,13 @@ class RoutedExperts(Part):
         self.experts = int(p["experts"])
         self.top = int(p["top"])
         self.ff = int(p["ff"])
-        self.limit = float(p["limit"])
+        self.limit = float(p["limit"]) if p.get("limit") is not None else float("inf")
         self.alpha = float(p.get("alpha", 1.702))
         self.shift = float(p.get("shift", 1.0))
         self.router_bias = bool(p.get("router_bias", True))
         shared = p.get("shared")
         self.shared_ff = int(shared["ff"]) if shared else 0
-        self.shared_limit = float(shared["limit"]) if shared else 0.0
+        self.shared_limit = (float(shared["limit"]) if shared.get("limit") is not None else float("inf")) if shared else 0.0
         self.shared_gated = bool(shared.get("gate", True)) if shared else False
         if not 1 <= self.top <= min(self.experts, 32):
             raise ValueError(f"moe: top {self.top} of {self.experts} experts is not supported (1 to 32, at most all)")

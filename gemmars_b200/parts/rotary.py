@@ -6,10 +6,18 @@ the pair (a, b) -> (a cos - b sin, b cos + a sin) (src/kernels.rs:1538-1548).  W
 pair i is the ``layout``: "half" pairs v[i] with v[i + rotary_dim / 2] (the default), "interleaved"
 pairs v[2i] with v[2i + 1].
 
+``scaling`` (default none) stretches the long wavelengths for contexts beyond the trained one,
+{"factor", "low", "high", "original"}: with l = 2 pi / f the wavelength of a frequency f, f stays
+where l < original / high, becomes f / factor where l > original / low, and in between is the
+blend (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  The table is made
+once, in float64, and rounded to float32.
+
 The attention part fuses the "half" rotation into its q/k kernel when its position encoding is
 this class, and the latent attention part the "interleaved" one into the kernel that writes its
 cache rows; ``apply`` is the stand-alone form of either."""
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -31,9 +39,30 @@ class Rotary(Part):
         if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary: cannot rotate {self.rotary_dim} of {self.head_dim} dimensions")
         i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
-        self._inv_freq_host = (1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64),
-                                               2.0 * i / max(self.rotary_dim, 1))).to(torch.float32)
+        freq = 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64), 2.0 * i / max(self.rotary_dim, 1))
+        self.scaling = spec.params.get("scaling")
+        if self.scaling:
+            freq = self.scaled(freq, self.scaling)
+        self._inv_freq_host = freq.to(torch.float32)
         self._inv_freq = {}
+
+    @staticmethod
+    def scaled(freq: torch.Tensor, scaling: dict) -> torch.Tensor:
+        """``freq`` (float64) with its long wavelengths stretched as ``scaling`` says."""
+        try:
+            factor, low, high, original = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+        except (KeyError, TypeError, ValueError):
+            raise ValueError(f"rotary: scaling needs the numbers factor, low, high and original, got {scaling!r}") from None
+        if factor <= 0 or original <= 0 or high <= 0 or low <= 0:
+            raise ValueError(f"rotary: scaling factor, low, high and original must be positive, got {scaling!r}")
+        wavelength = 2.0 * math.pi / freq
+        if high == low:
+            blend = freq
+        else:
+            s = (original / wavelength - low) / (high - low)
+            blend = (1.0 - s) * freq / factor + s * freq
+        out = torch.where(wavelength > original / low, freq / factor, blend)
+        return torch.where(wavelength < original / high, freq, out)
 
     def inv_freq(self, device) -> torch.Tensor:
         t = self._inv_freq.get(device)
@@ -48,7 +77,7 @@ class Rotary(Part):
         """(cos, sin) of the step's packed tokens' angles, [tokens, rotary_dim / 2, 2] float32,
         computed once a step and shared by every layer with the same rotation."""
         assert self.layout == "half"
-        key = ("rope_table", self.rotary_dim, self.theta)
+        key = ("rope_table", self.rotary_dim, self.theta, repr(self.scaling))
         t = ctx.extras.get(key)
         if t is None:
             t = ctx.extras[key] = kernels.rope_table(ctx.tok_pos, self.inv_freq(ctx.device))

@@ -23,7 +23,10 @@ from .safetensors_io import write_safetensors
 _STD = {"matrix": (0.0, 0.02), "bias": (0.0, 0.02), "norm": (1.0, 0.1),
         # weights kept around zero (a norm stored as a deviation from one, a step-size bias), the taps
         # of a short filter over time, and the logarithm of a decay rate
-        "small": (0.0, 0.1), "filter": (0.0, 0.4), "log_rate": (0.0, 0.5)}
+        "small": (0.0, 0.1), "filter": (0.0, 0.4), "log_rate": (0.0, 0.5),
+        # the share of the token before in a blend of two tokens, the logarithm of a decay's rate before its
+        # low-rank part, the bonus of a token's own key, and the second matrix of a low-rank pair
+        "blend": (0.5, 0.2), "decay_base": (-1.0, 0.7), "bonus": (0.3, 0.3), "lowrank": (0.0, 0.15)}
 
 
 def _fnv1a(text: str) -> int:
