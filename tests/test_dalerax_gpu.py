@@ -1,0 +1,565 @@
+"""Dalerax on the GPU against the plain implementation: each mechanism's kernels alone, then whole
+models through the trace runner, the step function and the generation entry point, with prompts
+cut in every way, batches of unequal requests, reused slots and pages, planted keys far back, at
+page borders, on both sides of a window's edge and among the kept first tokens, sinks that take
+most of the weight and none, long decoding and the first tokens of a sequence."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_dalerax as plain
+from replay_util import Trace, run_trace
+from tiny_configs import DALERAX_A, DALERAX_B, DALERAX_C
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL_F32 = 3e-5
+# bfloat16 engine against the float64 plain implementation, as a fraction of the largest logit
+TOL_BF16 = 3e-2
+PAGE = 64
+
+
+def _dt(name):
+    return torch.float32 if name == "float32" else torch.bfloat16
+
+
+def _rand(rng, shape, dtype=torch.float32, scale=1.0, shift=0.0):
+    """Random values that ``dtype`` holds exactly, as (device tensor, float64 numpy)."""
+    t = torch.from_numpy(rng.standard_normal(shape) * scale + shift).to(dtype)
+    return t.to(DEV), t.double().numpy()
+
+
+def _i32(a):
+    return torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)
+
+
+def _packed(lens, slots, starts=None):
+    """Index tensors of a packed step: (cu_seqlens, tok_seq, seq_slot, tok_pos)."""
+    starts = starts or [0] * len(lens)
+    cu = np.concatenate([[0], np.cumsum(lens)])
+    seq = np.repeat(np.arange(len(lens)), lens)
+    pos = np.concatenate([np.arange(s, s + n) for s, n in zip(starts, lens)])
+    return _i32(cu), _i32(seq), _i32(slots), _i32(pos)
+
+
+def _cuts(total, sizes):
+    """[(start, end)] covering 0..total in portions of ``sizes`` (the last size repeats)."""
+    out, at, i = [], 0, 0
+    while at < total:
+        n = min(sizes[min(i, len(sizes) - 1)], total - at)
+        out.append((at, at + n))
+        at, i = at + n, i + 1
+    return out
+
+
+def _steps(lens, sizes):
+    """Walks sequences of ``lens`` tokens side by side in portions of ``sizes``: yields, step by
+    step, [(sequence, lo, hi)] of the sequences that still have tokens."""
+    cuts = [_cuts(n, sizes) for n in lens]
+    for step in range(max(len(c) for c in cuts)):
+        yield [(i, *cuts[i][step]) for i in range(len(lens)) if step < len(cuts[i])]
+
+
+# ------------------------------------------------------------------ mechanisms alone
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width,n_mix", [(52, 5), (1100, 2), (128, 1)])
+def test_blends_with_the_token_before(dtype, width, n_mix):
+    """Three sequences in other slots than their order; portions of 1, 2, 3 and 7 rows and single
+    rows; the row before a sequence's first is zeros, before a portion's first the last row of the
+    portion before; a slot that is cleared and used again."""
+    from gemmars_b200 import kernels
+    rng = np.random.default_rng(width)
+    lens, slots = [23, 1, 9], [2, 0, 3]
+    mu, mun = _rand(rng, (n_mix, width), scale=0.3, shift=0.5)
+    seqs = [_rand(rng, (n, width + 6), _dt(dtype)) for n in lens]
+    want = [np.stack([x[:, 3:3 + width] + (plain.shifted(x[:, 3:3 + width]) - x[:, 3:3 + width]) * mun[s] for s in range(n_mix)])
+            for _, x in seqs]
+    state = torch.zeros((5, width), dtype=torch.float32, device=DEV)
+    state[1] = 7.0                                   # a slot nobody uses keeps what it held
+    for round_ in range(2):
+        for sizes in ([1000], [1, 2, 3, 7], [1]):
+            got = [np.zeros((n_mix, n, width)) for n in lens]
+            for live in _steps(lens, sizes):
+                rows = torch.cat([seqs[i][0][lo:hi] for i, lo, hi in live])
+                cu, seq, slot, _ = _packed([hi - lo for _, lo, hi in live], [slots[i] for i, _, _ in live])
+                out = kernels.shift_mix(rows[:, 3:3 + width], mu, state, cu, seq, slot).double().cpu().numpy()
+                at = 0
+                for i, lo, hi in live:
+                    got[i][:, lo:hi] = out[:, at:at + hi - lo]
+                    at += hi - lo
+            for i in range(3):
+                tol = 1e-6 if dtype == "float32" else 1e-2
+                assert np.abs(got[i] - want[i]).max() < tol * max(1.0, np.abs(want[i]).max())
+                assert np.array_equal(state[slots[i]].double().cpu().numpy(), seqs[i][1][-1, 3:3 + width])
+            assert (state[1] == 7.0).all() and not state[4].any()
+            for s in slots:
+                state[s] = 0.0                       # what taking a slot again does
+
+
+@pytest.mark.parametrize("w_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tokens,channels,rank", [(1, 96, 16), (37, 72, 8), (300, 40, 5), (9, 1000, 1), (64, 256, 64)])
+def test_decay_from_its_two_matrices(w_dtype, tokens, channels, rank):
+    from gemmars_b200 import kernels
+    rng = np.random.default_rng(rank)
+    z, zn = _rand(rng, (tokens, rank), scale=1.5)
+    w2, w2n = _rand(rng, (channels, rank), _dt(w_dtype), scale=0.5)
+    base, bn = _rand(rng, (channels,), scale=1.0, shift=-1.0)
+    got = kernels.lowrank_decay(z, w2, base).double().cpu().numpy()
+    want = np.exp(-np.exp(np.tanh(zn) @ w2n.T + bn))
+    assert got.shape == want.shape and np.abs(got - want).max() < 2e-6
+    assert want.min() < 0.3 and want.max() > 0.9          # the decays of the test spread over their range
+
+
+@pytest.mark.parametrize("heads,dim", [(3, 24), (1, 40), (2, 64), (2, 128), (4, 16), (1, 200), (2, 33)])
+def test_decayed_linear_attention_alone(heads, dim):
+    """Whole sequences against portions of 1, 2, 5 and 33 tokens and token by token, in slots out of
+    order.  One k of a sequence is made large on channels whose decay is held at one, with a
+    distinctive v, and a query hundreds of tokens later points at it: the read-out must find that
+    write, whole and however the walk was cut."""
+    from gemmars_b200 import kernels
+    rng = np.random.default_rng(heads * 100 + dim)
+    lens, slots = [260, 2, 40], [1, 3, 0]
+    n_ch = heads * dim
+    bonus, un = _rand(rng, (heads, dim), scale=0.5, shift=0.3)
+    data, want = [], []
+    for n in lens:
+        x, xn = _rand(rng, (n, 3 * n_ch + 5), scale=0.5)
+        v, vn = _rand(rng, (n, n_ch + 2))
+        xn[:, 2 * n_ch:3 * n_ch] = np.exp(-np.exp(xn[:, 2 * n_ch:3 * n_ch] * 2.0 - 1.0))     # decays in (0, 1)
+        if n > 200:
+            xn[:, 2 * n_ch:2 * n_ch + 4] = 1.0                   # the first channels of head 0 forget nothing
+            xn[5, n_ch:n_ch + 4] = 30.0                          # a loud key at token 5 ...
+            xn[5 + 1:, n_ch:n_ch + 4] *= 0.01
+            xn[250, :4] = 2.0                                    # ... that the query at 250 asks for
+            xn[250, 4:dim] *= 0.01
+            vn[5, :dim] = np.arange(dim) - 3.0
+        x, v = torch.from_numpy(xn).float().to(DEV), torch.from_numpy(vn).float().to(DEV)
+        xn = x.double().cpu().numpy()
+        data.append((x, v))
+        r, k, w = (xn[:, j * n_ch:(j + 1) * n_ch].reshape(n, heads, dim) for j in range(3))
+        want.append(plain.wkv_scan(r, k, vn[:, :n_ch].reshape(n, heads, dim), w, un))
+    y250 = want[0][0][250, 0]
+    assert np.abs(y250 - 240.0 * (np.arange(dim) - 3.0)).max() < 0.2 * 240.0 * dim      # the planted write dominates the read
+    for sizes in ([1000], [1, 2, 5, 33], [1]):
+        state = torch.zeros((5, heads, kernels.recurrent_state_floats(dim, dim)), dtype=torch.float32, device=DEV)
+        got = [np.zeros((n, n_ch)) for n in lens]
+        for live in _steps(lens, sizes):
+            x = torch.cat([data[i][0][lo:hi] for i, lo, hi in live])
+            v = torch.cat([data[i][1][lo:hi] for i, lo, hi in live])
+            cu, seq, slot, _ = _packed([hi - lo for _, lo, hi in live], [slots[i] for i, _, _ in live])
+            y = torch.empty((x.shape[0], n_ch), dtype=torch.float32, device=DEV)
+            kernels.wkv_scan(x[:, :n_ch], x[:, n_ch:2 * n_ch], x[:, 2 * n_ch:3 * n_ch], v[:, :n_ch], bonus, state, cu, slot, y,
+                             heads, dim, dim)
+            res, at = y.double().cpu().numpy(), 0
+            for i, lo, hi in live:
+                got[i][lo:hi] = res[at:at + hi - lo]
+                at += hi - lo
+        for i, (out, final) in enumerate(want):
+            assert np.abs(got[i] - out.reshape(lens[i], -1)).max() < 2e-5 * max(1.0, np.abs(out).max())
+            held = torch.stack([kernels.recurrent_state_matrix(state[slots[i], h], dim, dim) for h in range(heads)])
+            assert np.abs(held.double().cpu().numpy() - final).max() < 2e-5 * max(1.0, np.abs(final).max())
+        assert not state[2].any() and not state[4].any()
+    kernels.check_status()
+
+
+class _Ctx:
+    """What attention_capped reads of a step's context: every query a sequence of its own that
+    brings one token, all of them reading the same slot."""
+
+    def __init__(self, positions, slot):
+        n = len(positions)
+        self.tok_pos, self.tok_seq, self.seq_slot = _i32(positions), _i32(np.arange(n)), _i32([slot] * n)
+        self.cu_seqlens, self.seq_start, self.n_seqs = _i32(np.arange(n + 1)), _i32(positions), n
+
+
+class _PromptCtx:
+    """One sequence that brings the rows lo..hi of slot ``slot`` in one step."""
+
+    def __init__(self, lo, hi, slot):
+        self.cu_seqlens, self.tok_seq, self.seq_slot, self.tok_pos = _packed([hi - lo], [slot], [lo])
+        self.seq_start, self.n_seqs = _i32([lo]), 1
+
+
+SCALING = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64.0}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,groups,dim,vdim,rot,window,keep",
+                         [(4, 2, 32, 16, 16, 20, 3), (3, 3, 16, 24, 0, 7, 0), (8, 4, 64, 128, 32, 130, 70), (2, 1, 128, 128, 128, 200, 5),
+                          (6, 2, 64, 64, 64, 64, 1), (2, 2, 48, 80, 8, 33, 65), (5, 1, 20, 12, 4, 17, 2), (4, 1, 64, 64, 32, 400, 4)])
+def test_sink_attention_finds_planted_keys(dtype, heads, groups, dim, vdim, rot, window, keep):
+    """One sequence of 300 tokens in shuffled pages beside a short one.  The rotation (with stretched
+    wavelengths) is checked through the q rows and the cache rows; then queries are built that
+    point at single keys: far back, on both sides of page borders, the query's own position, the
+    keys just inside and just outside the window, and the last kept token and the first that is
+    not kept.  One head's sink is louder than any key, one's far below all, the others' in
+    between.  The queries run one by one (the form of decoding) and as rows of prompts cut in
+    portions."""
+    from gemmars_b200 import kernels
+    rng = np.random.default_rng(dim + vdim)
+    dt = _dt(dtype)
+    n, short = 300, 5
+    channels = (heads + groups) * dim + groups * vdim
+    scale = 0.2
+    freq = plain.rotary_frequencies(5000.0, rot, SCALING) if rot else np.zeros(0)
+    inv = torch.tensor(freq, dtype=torch.float32, device=DEV)
+    table = torch.tensor([[7, 2, 9, 4, 1], [3, 0, 0, 0, 0], [0, 0, 0, 0, 0]], dtype=torch.int32, device=DEV)
+    u, un = _rand(rng, (n + short, channels + 8), dt)
+    f = [un[:n, 4:4 + channels], un[n:, 4:4 + channels]]
+    want_q, want_k, want_v = [], [], []
+    for x in f:
+        t = len(x)
+        want_q.append(plain.rotate_half(x[:, :heads * dim].reshape(t, heads, dim), np.arange(t), freq))
+        want_k.append(plain.rotate_half(x[:, heads * dim:(heads + groups) * dim].reshape(t, groups, dim), np.arange(t), freq))
+        want_v.append(x[:, (heads + groups) * dim:].reshape(t, groups, vdim))
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    for sizes in ([1000], [2, 3, 64, 1, 65], [1]):
+        kc = torch.zeros((11, groups, PAGE, dim), dtype=dt, device=DEV)
+        vc = torch.zeros((11, groups, vdim, PAGE), dtype=dt, device=DEV)
+        q_all = torch.zeros((n + short, heads * dim), dtype=dt, device=DEV)
+        for live in _steps([n, short], sizes):
+            spans = [(lo + (n if i else 0), hi + (n if i else 0)) for i, lo, hi in live]
+            rows = torch.cat([u[lo:hi] for lo, hi in spans])
+            cu, seq, slot, pos = _packed([hi - lo for _, lo, hi in live], [i for i, _, _ in live], [lo for _, lo, _ in live])
+            q = torch.empty((rows.shape[0], heads * dim), dtype=dt, device=DEV)
+            kernels.filter_rope_cache(rows[:, 4:4 + channels], None, None, inv if rot else None, rot, pos, seq, slot, cu, table,
+                                      PAGE, q, kc, vc, heads, groups, dim, vdim)
+            at = 0
+            for lo, hi in spans:
+                q_all[lo:hi] = q[at:at + hi - lo]
+                at += hi - lo
+        got_q = q_all.double().cpu().numpy()
+        assert np.abs(got_q[:n].reshape(n, heads, dim) - want_q[0]).max() < tol * 4
+        assert np.abs(got_q[n:].reshape(short, heads, dim) - want_q[1]).max() < tol * 4
+        kh, vh, th = kc.double().cpu().numpy(), vc.double().cpu().numpy(), table.cpu().numpy()
+        for p in (0, 1, 63, 64, 65, 127, 128, 255, 256, 299):
+            assert np.abs(kh[th[0, p // PAGE], :, p % PAGE] - want_k[0][p]).max() < tol * 4
+            assert np.abs(vh[th[0, p // PAGE], :, :, p % PAGE] - want_v[0][p]).max() < tol * 4
+        assert not kh[5].any() and not kh[6].any() and not kh[0].any()       # pages nobody owns
+    # queries that point at single keys of the long sequence, as the cache holds them
+    keys = kh
+    targets = set()
+    for p in (299, 200, 128, 64, 17, keep, max(keep - 1, 0), 0, 1):
+        for j in (p, p - 1, p - p % PAGE, p - p % PAGE - 1, 0, p - window + 1, p - window, p - window - 1, p - window + 2,
+                  keep - 1, keep, keep + 1, 63, 64):
+            if 0 <= j <= p:
+                targets.add((p, j))
+    targets = sorted(targets)
+    qn = np.zeros((len(targets), heads, dim))
+    for i, (p, j) in enumerate(targets):
+        for h in range(heads):
+            key = keys[th[0, j // PAGE], h // (heads // groups), j % PAGE]
+            qn[i, h] = key * (40.0 / scale / max((key * key).sum(), 1e-3))    # a score of 40 for key j
+    q = torch.from_numpy(qn.reshape(len(targets), -1)).to(dt).to(DEV)
+    sink_n = rng.standard_normal(heads) * 3.0 + 30.0
+    sink_n[0] = 48.0                                 # louder than the planted key: most of the weight is lost
+    sink_n[-1] = -60.0                               # as good as no sink
+    sink = torch.tensor(sink_n, dtype=torch.float32, device=DEV)
+    sink_n = sink.double().cpu().numpy()
+    kall = np.stack([keys[th[0, j // PAGE], :, j % PAGE] for j in range(n)])
+    vall = np.stack([vh[th[0, j // PAGE], :, :, j % PAGE] for j in range(n)])
+    want = plain.sink_attention(q.double().cpu().numpy().reshape(len(targets), heads, dim), kall, vall, [p for p, _ in targets],
+                                np.arange(n), scale, window, keep, sink_n).reshape(len(targets), -1)
+    atol = (2e-5 if dtype == "float32" else 2e-2) * max(1.0, np.abs(want).max())
+
+    def run(ctx, rows, mma=True):
+        out = torch.empty((rows.shape[0], heads * vdim), dtype=dt, device=DEV)
+        kernels.CAPPED_ATTENTION_MMA = mma
+        try:
+            kernels.attention_capped(ctx, rows, out, heads, kc, vc, table, PAGE, window, scale, 0.0, None, 1.0, keep, sink)
+        finally:
+            kernels.CAPPED_ATTENTION_MMA = True
+        return out.double().cpu().numpy()
+
+    ctx = _Ctx([p for p, _ in targets], 0)
+    out = run(ctx, q)
+    assert np.abs(out - want).max() < atol
+    if kernels.attention_capped_mma_usable(dt, dim, vdim, PAGE):
+        assert np.abs(run(ctx, q, mma=False) - want).max() < atol          # the plain kernel on the same inputs
+    # the planted key decides: a key the mask hides never gives the output its value; one it shows does
+    found = 0
+    for i, (p, j) in enumerate(targets):
+        seen = plain.visible(p, j, window, keep)
+        for h in range(1, heads):
+            mine = vall[j, h // (heads // groups)]
+            close = np.abs(out[i].reshape(heads, vdim)[h] - mine).max() < 0.1 * np.abs(mine).max()
+            assert not (close and not seen), f"query {p} saw key {j} outside its window of {window} and {keep} kept"
+            found += bool(close and seen)
+    assert found >= 0.8 * sum(plain.visible(p, j, window, keep) for p, j in targets) * (heads - 1)
+    assert np.abs(out.reshape(len(targets), heads, vdim)[:, 0]).max() < 0.01 * np.abs(vall).max() + atol      # the loud sink's head
+    # the same queries as rows of a prompt: the row at position p of a step that brings lo..hi
+    for sizes in ([1000], [2, 3, 64, 1, 65], [31]):
+        rows = torch.zeros((n, heads * dim), dtype=dt, device=DEV)
+        last = {}
+        for i, (p, j) in enumerate(targets):
+            last[p] = i
+        for p, i in last.items():
+            rows[p] = q[i]
+        got = np.zeros((n, heads * vdim))
+        for lo, hi in _cuts(n, sizes):
+            got[lo:hi] = run(_PromptCtx(lo, hi, 0), rows[lo:hi])
+        for p, i in last.items():
+            assert np.abs(got[p] - want[i]).max() < atol, (p, targets[i])
+    kernels.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("t,width,experts,top,ff,ffs", [(9, 72, 5, 2, 40, 24), (200, 128, 8, 3, 64, 96), (2, 52, 2, 1, 20, 0),
+                                                      (130, 64, 4, 4, 32, 0), (70, 72, 3, 1, 48, 16)])
+def test_routed_feed_forward_without_clamps(dtype, t, width, experts, top, ff, ffs):
+    """The routed part as this design configures it (plain gated experts, a router with a bias,
+    softmax over the chosen logits, a shared expert that is simply added) against the plain one."""
+    from gemmars_b200.parts.base import build_part
+    from gemmars_b200.parts.plan import PartSpec
+    rng = np.random.default_rng(t)
+    dt = _dt(dtype)
+    names, w, wn = {}, {}, {}
+
+    def add(short, shape, scale):
+        w[short], wn[short.replace("router_bias", "router.b")] = _rand(rng, shape, dt, scale)
+        names[short] = short
+    add("router", (experts, width), 0.3)
+    add("router_bias", (experts,), 0.5)
+    for e in range(experts):
+        for part, shape in (("gate", (ff, width)), ("up", (ff, width)), ("down", (width, ff))):
+            add(f"e{e}.{part}", shape, 0.2)
+    if ffs:
+        for part, shape in (("gate", (ffs, width)), ("up", (ffs, width)), ("down", (width, ffs))):
+            add(f"shared.{part}", shape, 0.2)
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}, "shared": {"ff": ffs} if ffs else None}
+    part = build_part("ffn", PartSpec("moe", {"hidden_size": width, "experts": experts, "top": top, "ff": ff, "limit": None,
+                                              "alpha": 1.0, "shift": 0.0, "router_bias": True,
+                                              "shared": {"ff": ffs, "limit": None, "gate": False} if ffs else None}, names), dtype)
+    part.load({k: (v.float() if part.wants()[k].role == "vector" else v.to(dt)) for k, v in w.items()})
+    h, hn = _rand(rng, (t, width), dt)
+    res, resn = _rand(rng, (t, width), torch.float32)
+    part.forward(type("Ctx", (), dict(host=None))(), h, res)
+    want = resn + plain.routed_ffn(hn, wn, mlp)
+    # a token whose last chosen and first unchosen logits are closer than rounding may go either way
+    z = np.sort(hn @ wn["router"].T + wn["router.b"], axis=1)[:, ::-1]
+    sure = np.ones(t, bool) if top == experts else (z[:, top - 1] - z[:, top]) > (1e-4 if dtype == "float32" else 0.05)
+    tol = 2e-5 if dtype == "float32" else 1.5e-2
+    assert sure.mean() > 0.8
+    assert np.abs(res.double().cpu().numpy() - want)[sure].max() <= tol * np.abs(want).max()
+
+
+# ------------------------------------------------------------------ whole models
+
+def _sharp_folder(tmp_path_factory, raw, seed, factor):
+    """Random weights whose query and key matrices are scaled by ``factor``: scores grow with its
+    square, the softmax picks single keys (or the sink) instead of averaging, and a wrong key, a
+    window that is off by one, a missing sink, a wrong page or slot shows in the logits."""
+    from gemmars_b200.weights import random_weights, write_safetensors
+    tensors = random_weights(raw, seed=seed)
+    for name in tensors:
+        if name.endswith((".mix.q", ".mix.k")) and name.replace(".mix.k", ".mix.q").replace(".mix.q", ".mix.sink") in tensors:
+            tensors[name] = (tensors[name].float() * factor).bfloat16()
+    d = str(tmp_path_factory.mktemp("dalerax"))
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(raw, f)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    return d
+
+
+def _within(errors, tol, dtype, what):
+    """float32: every position within ``tol``.  bfloat16: rounding the router's input moves a token
+    whose candidate experts have nearly equal logits to another expert now and then, which changes
+    that position's logits (and through the recurrent state, a few after it) by more than rounding;
+    up to 4 % of the positions (at least one) may be over, and the rest must be within ``tol``."""
+    errors = np.asarray(errors)
+    over = int((errors > tol).sum())
+    allowed = 0 if dtype == "float32" else max(1, int(0.04 * errors.size))
+    assert over <= allowed, f"{what}: {over} of {errors.size} positions are over {tol:.2e} (worst {errors.max():.2e})"
+
+
+# A: windows of 20, 7 and 33 with 3, 0 and 1 kept tokens; B: a window of 130 beside 70 kept, 64 and 200
+REQUESTS = {"A": (DALERAX_A, [15, 21, 9, 70, 44, 131]), "B": (DALERAX_B, [17, 33, 3, 80, 150, 270])}
+GROUPS = [[0, 1, 2], [3, 4, 5]]
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for name, (raw, lengths) in REQUESTS.items():
+        folder = _sharp_folder(tmp_path_factory, raw, seed=21 + len(name), factor=9.0)
+        cfg, w = plain.load_folder(folder)
+        rng = np.random.default_rng(lengths[0])
+        reqs = [rng.integers(0, raw["vocab"], n).tolist() for n in lengths]
+        out[name] = (folder, cfg, w, reqs, [plain.forward(cfg, w, r) for r in reqs])
+    return out
+
+
+def test_the_test_models_attend_sharply(models):
+    """The scaled queries and keys do what they are for: in the plain model, hiding the one key
+    just inside a window's edge, or dropping the sinks, moves the logits by far more than any
+    tolerance used here."""
+    folder, cfg, w, reqs, ref = models["A"]
+    toks = reqs[5]
+    narrower = json.loads(json.dumps(cfg))
+    for layer in narrower["layers"]:
+        if layer["type"] == "attention":
+            layer["mixer"]["mask"]["size"] -= 1
+    no_sink = {k: (v - 60.0 if k.endswith(".sink") else v) for k, v in w.items()}
+    fewer_kept = json.loads(json.dumps(cfg))
+    fewer_kept["layers"][1]["mixer"]["mask"]["keep_first"] -= 1
+    scale = np.abs(ref[5]).max()
+    for other in (plain.forward(narrower, w, toks), plain.forward(cfg, no_sink, toks), plain.forward(fewer_kept, w, toks)):
+        moved = np.abs(other - ref[5]).max(axis=1)
+        assert moved.max() > 3 * TOL_BF16 * scale and (moved[40:] > 100 * TOL_F32 * scale).mean() > 0.3
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_all_cuttings_match_the_plain_implementation(name, dtype, models, tmp_path):
+    """Through bin/trace_run: each request whole, with its last 40 tokens one by one (every window
+    of A passes over decoded tokens), and in two batches of unequal requests that follow one another
+    in a cache sized to the peak, so that the second batch lives in the slots and pages the first
+    gave back."""
+    folder, cfg, w, reqs, ref = models[name]
+    tr = Trace()
+    tr.whole("w", reqs)
+    tr.tail("t", reqs, n_tail=40)
+    prompt_lens = [max(1, len(r) - 8 - 3 * i) for i, r in enumerate(reqs)]
+    prompt_lens[2] = len(reqs[2])
+    prompt_lens[1] = 1
+    tr.batches("b", reqs, GROUPS, prompt_lens)
+    got = run_trace(tr, folder, dtype, str(tmp_path / "out"))
+    scale = max(float(np.abs(r).max()) for r in ref)
+    tol = (TOL_F32 if dtype == "float32" else TOL_BF16) * scale
+    for tag in "wtb":
+        _within([np.abs(got[(f"{tag}{i}", p)] - r[p]).max() for i, r in enumerate(ref) for p in range(len(r))], tol, dtype,
+                f"cutting {tag!r}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_residual_after_every_layer(dtype, models):
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    folder, cfg, w, reqs, _ = models["A"]
+    toks = reqs[3]
+    _, want = plain.forward(cfg, w, toks, return_layers=True)
+    model = build_model(folder, dtype=dtype)
+    seen = []
+    for block in model.blocks:
+        def run(ctx, x, caches, writes_cache=True, _inner=block.forward):
+            _inner(ctx, x, caches, writes_cache=writes_cache)
+            assert x.dtype == torch.float32                      # the residual stream is 32-bit in both modes
+            seen.append(x.double().cpu().numpy())
+        block.forward = run
+    runner = Runner(model, max_tokens=256, max_batch=1, use_graphs=False)
+    runner.step([StepItem(runner.open(), toks, [])])
+    assert len(seen) == len(want)
+    for i, (a, b) in enumerate(zip(seen, want)):
+        tol = (1e-5 if dtype == "float32" else 2e-2) * np.abs(b).max()
+        _within(np.abs(a - b).max(axis=1), tol, dtype, f"layer {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portions_long_decoding_and_reused_slots(dtype, models):
+    """One runner, a cache of eight pages.  A prompt in portions of 2, 3, 64, 1, 65 and the rest;
+    another from its first token one by one for 300 steps, across four page borders, past the
+    window of 130 and the 70 kept tokens, beside a neighbour that comes and goes; then the same
+    again in the slots and pages given back: in float32 to the last bit."""
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    folder, cfg, w, reqs, ref = models["B"]
+    model = build_model(folder, dtype=dtype)
+    runner = Runner(model, max_tokens=8 * PAGE, max_batch=3)
+    rng = np.random.default_rng(8)
+    long_toks = rng.integers(0, cfg["vocab"], 300).tolist()
+    long_ref = plain.forward(cfg, w, long_toks)
+    scale = float(np.abs(long_ref).max())
+    tol = (TOL_F32 if dtype == "float32" else TOL_BF16) * scale
+    first_round = None
+    for round_ in range(2):
+        got = {}
+        a = runner.open()
+        at = 0
+        for n in (2, 3, 64, 1, 65, 15):
+            part = reqs[4][at:at + n]
+            got.update({("a", at + i): r for i, r in enumerate(runner.step([StepItem(a, part, range(len(part)))]).cpu().numpy())})
+            at += len(part)
+        assert at == len(reqs[4])
+        runner.close(a)
+        b = runner.open()
+        c = None
+        for p, tok in enumerate(long_toks):
+            items = [StepItem(b, [tok], [0])]
+            if p == 20:
+                c = runner.open()
+                items.append(StepItem(c, reqs[0], range(len(reqs[0]))))     # a prompt beside a decoded token
+            elif c is not None and p < 20 + 30:
+                items.append(StepItem(c, [reqs[1][p - 21]], [0]))
+            out = runner.step(items).cpu().numpy()
+            got[("b", p)] = out[0]
+            if p == 20:
+                got.update({("c", i): r for i, r in enumerate(out[1:])})
+            if p == 49:
+                runner.close(c)
+                c = None
+        runner.close(b)
+        assert runner.cache.pages_held() == 0
+        _within([np.abs(got[("a", p)] - ref[4][p]).max() for p in range(len(reqs[4]))], tol, dtype, "portions")
+        _within([np.abs(got[("b", p)] - long_ref[p]).max() for p in range(len(long_toks))], tol, dtype, "decoded")
+        _within([np.abs(got[("c", p)] - ref[0][p]).max() for p in range(len(reqs[0]))], tol, dtype, "neighbour")
+        if first_round is None:
+            first_round = got
+        elif dtype == "float32":
+            assert all(np.array_equal(got[k], first_round[k]) for k in got)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_the_tensor_cores_do_not_take(dtype, tmp_path_factory):
+    """A width of 52 and heads of 20 and 12: every product and the attention run on the plain
+    kernels.  Prompts in portions of two tokens, then token by token, against the whole."""
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    folder = _sharp_folder(tmp_path_factory, DALERAX_C, seed=5, factor=12.0)
+    cfg, w = plain.load_folder(folder)
+    rng = np.random.default_rng(13)
+    reqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in (61, 2, 30)]
+    ref = [plain.forward(cfg, w, r) for r in reqs]
+    scale = max(float(np.abs(r).max()) for r in ref)
+    runner = Runner(build_model(folder, dtype=dtype), max_tokens=4 * PAGE, max_batch=3)
+    slots = [runner.open() for _ in reqs]
+    errs = []
+    for live in _steps([len(r) for r in reqs], [2, 2, 2, 2, 1]):
+        out = runner.step([StepItem(slots[i], reqs[i][lo:hi], range(hi - lo)) for i, lo, hi in live]).cpu().numpy()
+        at = 0
+        for i, lo, hi in live:
+            errs += list(np.abs(out[at:at + hi - lo] - ref[i][lo:hi]).max(axis=1))
+            at += hi - lo
+    assert len(errs) == sum(len(r) for r in reqs)
+    _within(errs, (TOL_F32 if dtype == "float32" else TOL_BF16) * scale, dtype, "portions of two")
+    for s in slots:
+        runner.close(s)
+    assert runner.cache.pages_held() == 0
+
+
+def test_greedy_generation_through_the_engine(models):
+    from gemmars_b200 import Engine
+    folder, cfg, w, reqs, _ = models["A"]
+    eng = Engine.load(folder, "dtype=float32;max_batch=3;max_tokens=2048")
+    prompts = [reqs[0], reqs[2], [5], reqs[4][:33], reqs[3]]
+    free_run, _ = plain.generate(cfg, w, prompts[0], 10)
+    stop = [free_run[4]]
+    res = eng.generate(prompts, max_tokens=10, stop_ids=stop)
+    for p, r in zip(prompts, res):
+        want, reason = plain.generate(cfg, w, p, 10, stop=stop)
+        assert r.tokens == want and r.reason == reason
+    assert eng.runner.cache.pages_held() == 0
+    again = eng.generate(list(reversed(prompts)), max_tokens=10, stop_ids=stop)
+    assert [r.tokens for r in reversed(again)] == [r.tokens for r in res]
+    # bfloat16 decodes through captured steps: the tokens it picks are the plain model's best or within
+    # rounding of it (but for the few that follow a token routed to another expert, see _within)
+    eng16 = Engine.load(folder, "dtype=bfloat16;max_batch=4;max_tokens=2048")
+    near, total = 0, 0
+    for p, r in zip(prompts, eng16.generate(prompts, max_tokens=8, stop_ids=[])):
+        assert len(r.tokens) == 8
+        for i, tok in enumerate(r.tokens):
+            row = plain.forward(cfg, w, list(p) + r.tokens[:i])[-1]
+            near += bool(row[tok] >= row.max() - TOL_BF16 * np.abs(row).max())
+            total += 1
+    assert near >= 0.9 * total
+    assert eng16.runner.cache.pages_held() == 0

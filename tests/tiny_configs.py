@@ -168,3 +168,74 @@ KUPORAX_C = {
         _kuporax_parallel(_kuporax_left(2, 2, 20, 12, 2, 0.3, 5.0, 17, 50.0, 4), _kuporax_right(2, 10, 6, 2, 2, 3), 1.5, 0.8, 0),
     ],
 }
+
+
+def _dalerax_attention(heads, kv_heads, dim, vdim, scale, size, keep_first, base, dims, scaling=None, kv_from=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale,
+         "mask": {"size": size, "keep_first": keep_first}, "rot": {"base": base, "dims": dims}}
+    if scaling is not None:
+        m["rot"]["scaling"] = dict(zip(("factor", "low", "high", "original"), scaling))
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def _dalerax_moe(experts, top, ff, shared_ff):
+    return {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff},
+            "shared": {"ff": shared_ff} if shared_ff else None}
+
+
+def _dalerax_dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+# Dalerax: five layers that differ in every size.  It starts with a recurrent layer (three heads of
+# 24, a decay of rank 8); then attention with values narrower than keys, a window of 20 that keeps
+# the first 3 tokens, half of each head rotated with wavelengths in all three bands of the scaling;
+# then attention with as many kv heads as heads, values wider than keys, no rotation, a plain
+# window of 7 (its pages are a ring) and no feed-forward; then a layer that reads the second
+# layer's keys and values through a wider window that keeps one token, with every expert chosen and
+# no shared expert; last a recurrent layer of one head of 40 (more than a lane's 32) with one expert
+# of three.
+_A_ROT = (10000.0, 16, (4.0, 1.0, 4.0, 64.0))
+DALERAX_A = {
+    "architecture": "Dalerax", "vocab": 211, "width": 72, "max_positions": 700, "logit_scale": 1.3,
+    "embedding": {"scale": 3.0}, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "wkv", "mixer": {"heads": 3, "dim": 24, "rank": 8}, "mlp": _dalerax_dense(96)},
+        {"type": "attention", "mixer": _dalerax_attention(4, 2, 32, 16, 0.2, 20, 3, *_A_ROT), "mlp": _dalerax_moe(5, 2, 40, 24)},
+        {"type": "attention", "mixer": _dalerax_attention(4, 4, 16, 24, 0.3, 7, 0, 1.0, 0), "mlp": None},
+        {"type": "attention", "mixer": _dalerax_attention(4, 2, 32, 16, 0.15, 33, 1, *_A_ROT, kv_from=1),
+         "mlp": _dalerax_moe(4, 4, 32, 0)},
+        {"type": "wkv", "mixer": {"heads": 1, "dim": 40, "rank": 5}, "mlp": _dalerax_moe(3, 1, 48, 16)},
+    ],
+}
+
+# Dalerax with sizes the tensor-core kernels take and heads as wide as released models have: keys of
+# 64 with values of 128, a window of 130 beside 70 kept tokens (more than a page of them), a layer
+# that reads those keys through a window of 64 with nothing kept, a recurrent layer of heads of 64,
+# and full heads of 128 rotated without scaling under a window wider than most test sequences.
+DALERAX_B = {
+    "architecture": "Dalerax", "vocab": 520, "width": 128, "max_positions": 1024, "logit_scale": 1.0,
+    "embedding": {"scale": 11.3}, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "attention", "mixer": _dalerax_attention(8, 4, 64, 128, 0.125, 130, 70, 250000.0, 32, (8.0, 1.0, 4.0, 256.0)),
+         "mlp": _dalerax_dense(192)},
+        {"type": "wkv", "mixer": {"heads": 2, "dim": 64, "rank": 16}, "mlp": _dalerax_moe(8, 3, 64, 96)},
+        {"type": "attention", "mixer": _dalerax_attention(8, 4, 64, 128, 0.11, 64, 0, 250000.0, 32, (8.0, 1.0, 4.0, 256.0), kv_from=0),
+         "mlp": _dalerax_moe(8, 3, 64, 96)},
+        {"type": "attention", "mixer": _dalerax_attention(2, 1, 128, 128, 0.09, 200, 5, 1000.0, 128), "mlp": _dalerax_dense(160)},
+    ],
+}
+
+# A width that is no multiple of 8 and heads that are no multiple of 16: in bfloat16 the products and
+# the attention run on the plain kernels.  A scaling whose bands start at other places (low 2, high 3).
+DALERAX_C = {
+    "architecture": "Dalerax", "vocab": 97, "width": 52, "max_positions": 300, "logit_scale": 0.5,
+    "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "attention", "mixer": _dalerax_attention(2, 1, 20, 12, 0.22, 17, 2, 50.0, 4, (2.0, 2.0, 3.0, 40.0)),
+         "mlp": _dalerax_moe(2, 1, 20, 12)},
+        {"type": "wkv", "mixer": {"heads": 2, "dim": 12, "rank": 3}, "mlp": None},
+    ],
+}
