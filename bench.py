@@ -2,7 +2,7 @@
 """Decode and prefill throughput of Qwen3-shaped models with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference] [--config 8b|4b|32b]
-    python bench.py --compare toretar|kuporax [--sizes small,lite,mid] [--batch 8] [--context 4096]
+    python bench.py --compare toretar|kuporax|dalerax [--sizes small,lite,mid] [--batch 8] [--context 4096]
 
 ``--config 8b`` (the default) is the headline benchmark.  A step is one decode step of a batch
 of 8 sequences at a context of 8,192 tokens.  One JSON line is printed: ``value`` = decoded
@@ -110,11 +110,11 @@ def _value_dim(group):
     return group.need.head_dim if group.need.value_dim is None else group.need.value_dim
 
 
-def decode_bytes(model, runner, lengths):
+def decode_bytes(model, runner, lengths, cache_bytes=None):
     """Bytes one decode step has to read: every weight once and the cached keys and values of
-    the live sequences."""
+    the live sequences (``cache_bytes``: that share, where masks and not rings bound what is read)."""
     kv = 0
-    for g in runner.cache.kv_groups:
+    for g in (runner.cache.kv_groups if cache_bytes is None else ()):
         per_token = g.n_layers * g.need.num_kv_heads * (g.need.head_dim + _value_dim(g)) * g.k.element_size()
         for n in lengths:
             kv += per_token * (min(n, g.need.window) if g.need.window else n)
@@ -131,7 +131,7 @@ def decode_bytes(model, runner, lengths):
         for n in g.need.shape:
             per_seq *= n
         state += 2 * per_seq * len(lengths)
-    return model.weight_bytes() + extra + kv + state
+    return model.weight_bytes() + extra + kv + state + (cache_bytes or 0)
 
 
 def prefill_flops(cfg, t):
@@ -198,6 +198,52 @@ def kuporax_prefill_flops(cfg, t):
     return total + 2 * w * cfg["vocab"]
 
 
+def _dalerax_seen(mask, p):
+    """Keys position ``p`` sees: itself and the window before it, and the kept first ones the window has left."""
+    size, keep = mask["size"], mask.get("keep_first", 0)
+    return min(p + 1, size) + max(0, min(keep, p + 1 - size))
+
+
+def dalerax_prefill_flops(cfg, t):
+    """Floating-point operations of a prompt of ``t`` tokens from position 0: every product, the
+    scores and weighted values over the keys each token's mask lets it see, the decay's two small
+    products, the recurrence as it is written (one update and one read of the state a token,
+    4 dim dim a head), and for a routed feed-forward the router and the chosen experts."""
+    w, total = cfg["width"], 0
+    for i, layer in enumerate(cfg["layers"]):
+        m = layer["mixer"]
+        if layer["type"] == "attention":
+            own = 0 if "kv_from" in m else m["kv_heads"] * (m["dim"] + m["vdim"])
+            per_token = 2 * w * (m["heads"] * m["dim"] + own) + 2 * m["heads"] * m["vdim"] * w
+            pairs = 2 * m["heads"] * (m["dim"] + m["vdim"]) * sum(_dalerax_seen(m["mask"], p) for p in range(t))
+        else:
+            n, rank = m["heads"] * m["dim"], m.get("rank", 32)
+            per_token = 2 * w * (4 * n + rank) + 2 * rank * n + 2 * n * w + 4 * m["heads"] * m["dim"] * m["dim"]
+            pairs = 0
+        mlp = layer.get("mlp")
+        if mlp is not None and mlp["kind"] == "dense":
+            per_token += 6 * w * mlp["ff"]
+        elif mlp is not None:
+            per_token += 2 * w * mlp["router"]["experts"] + 6 * w * mlp["router"]["top"] * mlp["expert"]["ff"]
+            if mlp.get("shared"):
+                per_token += 6 * w * mlp["shared"]["ff"]
+        total += per_token * t + pairs
+    return total + 2 * w * cfg["vocab"]
+
+
+def dalerax_cache_bytes(cfg, lengths, element_size=2):
+    """Bytes of cached keys and values one decode step reads: every attention layer, also one that
+    reads another layer's cache, reads what its own mask sees."""
+    total = 0
+    for layer in cfg["layers"]:
+        if layer["type"] != "attention":
+            continue
+        m = layer["mixer"]
+        per_key = m["kv_heads"] * (m["dim"] + m["vdim"]) * element_size
+        total += sum(per_key * _dalerax_seen(m["mask"], n - 1) for n in lengths)
+    return total
+
+
 def fill_cache(runner, slots, length, real, vocab, gen):
     """Brings every slot to ``length`` cached tokens: by running prompts (real) or by
     reserving the pages and writing random keys and values (synthetic)."""
@@ -211,7 +257,7 @@ def fill_cache(runner, slots, length, real, vocab, gen):
     synthetic_fill(runner, slots, length)
 
 
-def time_decode(eng, batch, ctx_end, steps, warmup, real_fill, hbm_gbs):
+def time_decode(eng, batch, ctx_end, steps, warmup, real_fill, hbm_gbs, cfg=None):
     """Device time of exactly ``steps`` decode steps of ``batch`` sequences ending at ``ctx_end``,
     with the clocks sampled meanwhile: {"tokens_per_s", "ms_per_step", "steps", "bytes_per_step",
     "achieved_gbs", "frac", "clocks", "launches"}."""
@@ -256,7 +302,8 @@ def time_decode(eng, batch, ctx_end, steps, warmup, real_fill, hbm_gbs):
     ms = e0.elapsed_time(e1) / steps
     clock_rec = clocks.stop()
     lengths = [runner.length(s) for s in slots]
-    nbytes = decode_bytes(eng.model, runner, lengths)
+    masked = cfg is not None and cfg.get("architecture") == "Dalerax"
+    nbytes = decode_bytes(eng.model, runner, lengths, dalerax_cache_bytes(cfg, lengths) if masked else None)
     for s in slots:
         runner.close(s)
     kernels.check_status()
@@ -288,6 +335,8 @@ def time_prefill(eng, cfg, tokens, tflops, tflops_sustained):
     pre = statistics.median(pre_ms)
     if cfg.get("architecture") == "Kuporax":
         flops = kuporax_prefill_flops(cfg, tokens)
+    elif cfg.get("architecture") == "Dalerax":
+        flops = dalerax_prefill_flops(cfg, tokens)
     elif cfg.get("sliding_window") and cfg.get("use_sliding_window"):
         size = cfg["sliding_window"]      # a window on every layer: the keys a token sees, not the causal half
         seen = sum(min(p + 1, size) for p in range(tokens))
@@ -478,19 +527,21 @@ def kernel_table(eng, tokens, batch, context):
 
 
 def run_compare(args):
-    """Prompt and decode throughput of Toretar-shaped models beside Qwen3-shaped models of the same
-    width, depth and per-token feed-forward size, with a table of each one's kernels."""
-    from gemmars_b200.tuning import KUPORAX_PAIRS, PAIRS
-    pairs = KUPORAX_PAIRS if args.compare == "kuporax" else PAIRS
+    """Prompt and decode throughput of models of one architecture beside models of another with the
+    same width, depth and per-token feed-forward size (Toretar and Kuporax beside Qwen3, Dalerax
+    beside Kuporax), with a table of each one's kernels."""
+    from gemmars_b200.tuning import DALERAX_PAIRS, KUPORAX_PAIRS, PAIRS
+    pairs = {"kuporax": KUPORAX_PAIRS, "dalerax": DALERAX_PAIRS}.get(args.compare, PAIRS)
+    beside = "kuporax" if args.compare == "dalerax" else "qwen3"
     hbm_gbs, tflops, tflops_sustained, peak_src = peaks()
     sizes = [s for s in args.sizes.split(",") if s]
     out = {}
     for size in sizes:
         out[size] = {}
-        for arch, cfg in zip((args.compare, "qwen3"), pairs[size]):
+        for arch, cfg in zip((args.compare, beside), pairs[size]):
             eng = make_engine(cfg, args.batch, args.batch * (args.context + 64) + PREFILL_TOKENS + 64, args.options)
             rec = {"prefill": time_prefill(eng, cfg, PREFILL_TOKENS, tflops, tflops_sustained),
-                   "decode": time_decode(eng, args.batch, args.context, args.steps, max(3, args.warmup), False, hbm_gbs)}
+                   "decode": time_decode(eng, args.batch, args.context, args.steps, max(3, args.warmup), False, hbm_gbs, cfg)}
             if not args.no_points:
                 rec["kernels"] = kernel_table(eng, PREFILL_TOKENS, args.batch, args.context)
             out[size][arch] = rec
@@ -499,7 +550,7 @@ def run_compare(args):
             import torch
             gc.collect()
             torch.cuda.empty_cache()
-    return {"compare": f"{args.compare} beside qwen3", "sizes": out, "batch": args.batch, "context": args.context,
+    return {"compare": f"{args.compare} beside {beside}", "sizes": out, "batch": args.batch, "context": args.context,
             "prefill_tokens": PREFILL_TOKENS, "peaks": f"{hbm_gbs:.0f} GB/s, {tflops:.0f} TFLOP/s ({peak_src})",
             "dtype": "bf16", "data": "synthetic: random weights, random token ids, cache filled with random rows"}
 
@@ -520,8 +571,8 @@ def main():
     ap.add_argument("--e2e-tokens", type=int, default=E2E_TOKENS,
                     help="tokens a sequence generates in the end-to-end run (fewer for runs under a profiler)")
     ap.add_argument("--options", default="", help='further engine options, "key=value;key=value"')
-    ap.add_argument("--compare", choices=["toretar", "kuporax"], default=None,
-                    help="instead of the headline: models of that architecture beside Qwen3-shaped ones of equal size")
+    ap.add_argument("--compare", choices=["toretar", "kuporax", "dalerax"], default=None,
+                    help="instead of the headline: models of that architecture beside ones of equal size (Qwen3-shaped; Kuporax-shaped for dalerax)")
     ap.add_argument("--sizes", default="small,lite,mid", help="with --compare: which pairs of tuning.PAIRS")
     args = ap.parse_args()
     if args.impl == "reference":

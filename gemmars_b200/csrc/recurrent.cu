@@ -582,21 +582,50 @@ GB_EXPORT int gb_shift_mix(const void* x, int dtype, long long ldx, const float*
 // ------------------------------------------------------------------ decay from a low-rank projection
 // w[t, c] = exp(-exp(base[c] + sum_j W[c, j] tanh(z[t, j]))): the second half of a two-matrix decay
 // whose first product z = W1 x is made by the framework's product in float32.  tanh, the sum, both
-// exponentials and the result are float32; the rank is small (tens), so a thread takes a channel.
+// exponentials and the result are float32.  A block is 128 channels by DEC_TOK tokens: a thread
+// keeps a channel's sums for the block's tokens in registers and walks its row of W once, against
+// tanh(z) of the tokens in shared memory (DEC_RC entries of the rank a pass).  Every sum runs over
+// the rank in order with one accumulator, so the result does not depend on the tiling.
+constexpr int DEC_TOK = 8, DEC_RC = 128;
 template <typename T>
 __global__ void __launch_bounds__(128) lowrank_decay_kernel(const float* __restrict__ z, int rank, const T* __restrict__ W,
-                                                           const float* __restrict__ base, float* __restrict__ w, int C) {
-  extern __shared__ float th[];      // tanh(z[t, :])
+                                                           const float* __restrict__ base, float* __restrict__ w, int ntok, int C) {
+  __shared__ __align__(16) float th[DEC_TOK][DEC_RC];      // tanh(z[t0 + tt, j0 + j]), zeros beyond the edges
   pdl_release_next();
   pdl_wait_prior();
-  const int t = blockIdx.x;
-  for (int j = threadIdx.x; j < rank; j += blockDim.x) th[j] = tanhf(z[(size_t)t * rank + j]);
-  __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < rank; ++j) acc = fmaf(to_f32(W[(size_t)c * rank + j]), th[j], acc);
-    w[(size_t)t * C + c] = expf(-expf(acc + base[c]));
+  const int c = blockIdx.x * 128 + threadIdx.x, t0 = blockIdx.y * DEC_TOK;
+  const int n = min(DEC_TOK, ntok - t0);
+  const T* row = W + (size_t)min(c, C - 1) * rank;
+  float acc[DEC_TOK];
+#pragma unroll
+  for (int tt = 0; tt < DEC_TOK; ++tt) acc[tt] = 0.f;
+  for (int j0 = 0; j0 < rank; j0 += DEC_RC) {
+    const int nj = min(DEC_RC, rank - j0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < DEC_TOK * DEC_RC; i += 128) {
+      const int tt = i / DEC_RC, j = i % DEC_RC;
+      th[tt][j] = (tt < n && j < nj) ? tanhf(z[(size_t)(t0 + tt) * rank + j0 + j]) : 0.f;
+    }
+    __syncthreads();
+    for (int j = 0; j < nj; j += 4) {
+      float wv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) wv[e] = j + e < nj ? to_f32(row[j0 + j + e]) : 0.f;
+#pragma unroll
+      for (int tt = 0; tt < DEC_TOK; ++tt) {
+        const float4 h = *(const float4*)&th[tt][j];
+        acc[tt] = fmaf(wv[0], h.x, acc[tt]);
+        acc[tt] = fmaf(wv[1], h.y, acc[tt]);
+        acc[tt] = fmaf(wv[2], h.z, acc[tt]);
+        acc[tt] = fmaf(wv[3], h.w, acc[tt]);
+      }
+    }
   }
+  if (c >= C) return;
+  const float b = base[c];
+#pragma unroll
+  for (int tt = 0; tt < DEC_TOK; ++tt)
+    if (tt < n) w[(size_t)(t0 + tt) * C + c] = expf(-expf(acc[tt] + b));
 }
 
 // z: [ntok, rank] float32; W: [C, rank] float32 or bfloat16; base: [C]; w: [ntok, C] float32.
@@ -604,10 +633,12 @@ GB_EXPORT int gb_lowrank_decay(const float* z, int rank, const void* W, int w_dt
                                int C, cudaStream_t stream) {
   if (ntok <= 0) return 0;
   if (rank <= 0 || rank > 8192 || C <= 0) return GB_ERR_SIZE;
+  const dim3 grid((C + 127) / 128, (ntok + DEC_TOK - 1) / DEC_TOK);
+  if (grid.y > 65535) return GB_ERR_SIZE;
   if (w_dtype == GB_F32)
-    gb_launch(lowrank_decay_kernel<float>, dim3(ntok), 128, rank * sizeof(float), stream, z, rank, (const float*)W, base, w, C);
+    gb_launch(lowrank_decay_kernel<float>, grid, 128, 0, stream, z, rank, (const float*)W, base, w, ntok, C);
   else if (w_dtype == GB_BF16)
-    gb_launch(lowrank_decay_kernel<bf16>, dim3(ntok), 128, rank * sizeof(float), stream, z, rank, (const bf16*)W, base, w, C);
+    gb_launch(lowrank_decay_kernel<bf16>, grid, 128, 0, stream, z, rank, (const bf16*)W, base, w, ntok, C);
   else
     return GB_ERR_DTYPE;
   return gb_launch_status();

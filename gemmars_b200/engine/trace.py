@@ -30,7 +30,7 @@ from .step import Runner, StepItem
 
 
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None, report=None,
-           device: str = "cuda:0") -> int:
+           device: str = "cuda:0", spare_pages=None) -> int:
     lines = sys.stdin if lines is None else lines
     report = sys.stdout if report is None else report
     if not torch.cuda.is_available():
@@ -39,8 +39,12 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None
     torch.backends.cudnn.allow_tf32 = False
     os.makedirs(out_dir, exist_ok=True)
     model = build_model(model_dir, dtype=dtype, device=device)
+    # ``max_tokens`` counts the tokens themselves; every live request may also hold a page that is
+    # only partly used, so the cache gets a page more for each request it could hold at once
+    # (``spare_pages``; None: as many as there could be requests, 256 at most)
     pages = max(1, -(-max_tokens // PAGE_SIZE))
-    runner = Runner(model, max_tokens=max_tokens, max_batch=min(pages, 4096))
+    spare = min(max(1, max_tokens), 256) if spare_pages is None else max(0, int(spare_pages))
+    runner = Runner(model, max_tokens=(pages + spare) * PAGE_SIZE, max_batch=min(pages + spare, 4096))
     slots = {}
     for line in lines:
         line = line.strip()

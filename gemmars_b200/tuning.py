@@ -111,6 +111,45 @@ for _name, (_k, _q) in KUPORAX_PAIRS.items():
     PAIR_SHAPES[f"beside-kuporax-{_name}"] = (f"Qwen3 shape beside Kuporax '{_name}'", _q)
 
 
+def dalerax_shape(width, ff, heads, window, experts, top, order=("wkv", "attention", "attention", "wkv"),
+                  vocab=102400, positions=16384):
+    """A Dalerax config.json object: attention layers of ``heads`` heads of 128 (a quarter as many
+    kv heads, four kept first tokens, a sink, stretched long wavelengths), the second of which reads
+    the first one's keys and values; recurrent layers of heads of 64 over the whole width with a
+    decay of rank 64.  The first layer's feed-forward is dense; the others route ``top`` of
+    ``experts`` experts beside a shared one, sized so that a token passes ``ff`` hidden units in all."""
+    shared_ff = ff // 4
+    expert_ff = (ff - shared_ff) // top
+    rot = {"base": 1000000.0, "dims": 128, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    layers, first_attention = [], None
+    for i, kind in enumerate(order):
+        if kind == "wkv":
+            mixer = {"heads": width // 64, "dim": 64, "rank": 64}
+        else:
+            mixer = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                     "mask": {"size": window, "keep_first": 4}, "rot": rot}
+            if first_attention is None:
+                first_attention = i
+            else:
+                mixer["kv_from"] = first_attention
+        mlp = ({"kind": "dense", "ff": ff} if i == 0 else
+               {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}})
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Dalerax", "vocab": vocab, "width": width, "max_positions": positions, "logit_scale": 1.0,
+            "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "layers": layers}
+
+
+# Dalerax beside Kuporax, the nearest design the package has (recurrent layers around windowed
+# attention): the same width, depth, vocabulary, heads, window and hidden units a token passes
+DALERAX_PAIRS = {
+    "small": (dalerax_shape(1024, 4096, 8, 512, 16, 3), kuporax_shape(1024, 4096, 8, 512)),
+    "lite": (dalerax_shape(2048, 8192, 16, 1024, 32, 6), kuporax_shape(2048, 8192, 16, 1024)),
+    "mid": (dalerax_shape(4096, 12288, 32, 2048, 32, 6), kuporax_shape(4096, 12288, 32, 2048)),
+}
+for _name, (_d, _k) in DALERAX_PAIRS.items():
+    PAIR_SHAPES[f"dalerax-{_name}"] = (f"Dalerax shape '{_name}'", _d)
+
+
 def random_engine(cfg, max_batch, cache_tokens, options=""):
     """An engine over random weights of ``cfg`` made on the device; the tensors are taken out of
     their dict as they are bound, so that a model of 65 GB and its stacked q/k/v and gate/up copies

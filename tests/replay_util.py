@@ -74,11 +74,11 @@ class Trace:
         return "".join(json.dumps(s) + "\n" for s in self.steps)
 
 
-def run_trace(trace, model_dir, dtype, out_dir, max_tokens=None, timeout=600, env=None):
+def run_trace(trace, model_dir, dtype, out_dir, max_tokens=None, timeout=600, env=None, extra=()):
     """Runs bin/trace_run on the trace; returns {(request id, position): logits row}."""
     os.makedirs(out_dir, exist_ok=True)
     cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
-           "--max-tokens", str(max_tokens or trace.max_tokens())]
+           "--max-tokens", str(max_tokens or trace.max_tokens())] + list(extra)
     p = subprocess.run(cmd, input=trace.text(), capture_output=True, text=True, timeout=timeout, env=env)
     assert p.returncode == 0, f"trace_run failed ({p.returncode}):\n{p.stderr[-4000:]}"
     done = [l for l in p.stdout.splitlines() if l.startswith("done ")]

@@ -77,8 +77,9 @@ def test_pages_are_reused_within_a_tight_cache(oracle, tmp_path):
     tr = Trace()
     tr.batches("b", reqs, GROUPS, [len(r) // 2 + 1 for r in reqs])
     peak = tr.max_tokens()
-    got = run_trace(tr, folder, "float32", str(tmp_path / "tight"), max_tokens=peak)
+    tight = ["--spare-pages", "0"]       # no page beyond what max_tokens says
+    got = run_trace(tr, folder, "float32", str(tmp_path / "tight"), max_tokens=peak, extra=tight)
     for i, r in enumerate(ref):
         assert np.abs(got[(f"b{i}", len(r) - 1)] - r[-1]).max() <= TOL_F32 * 2
     with pytest.raises(AssertionError, match="does not fit in the cache|cache is full"):
-        run_trace(tr, folder, "float32", str(tmp_path / "short"), max_tokens=peak - 64)
+        run_trace(tr, folder, "float32", str(tmp_path / "short"), max_tokens=peak - 64, extra=tight)
