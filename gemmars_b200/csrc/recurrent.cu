@@ -503,11 +503,56 @@ __global__ void __launch_bounds__(128) gated_group_norm_kernel(const float* __re
   }
 }
 
+// The same for groups of at most 64 channels: a warp a group (eight groups a block), the sum by
+// shuffles, so that a token's row is not cut into blocks of one or two warps.
+template <typename O>
+__global__ void __launch_bounds__(256) gated_group_norm_warp_kernel(const float* __restrict__ y, const float* __restrict__ gate,
+                                                                   long long ldgate, const float* __restrict__ w, int wn,
+                                                                   O* __restrict__ out, int n, int gs, float eps, int gate_first,
+                                                                   float out_scale) {
+  pdl_release_next();
+  pdl_wait_prior();
+  const int t = blockIdx.x, group = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (group * gs >= n) return;
+  const int base = group * gs;
+  const float* row = y + (size_t)t * n + base;
+  const float* grow = gate + (size_t)t * ldgate + base;
+  float val[2], gt[2], ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int i = lane + 32 * e;
+    val[e] = i < gs ? row[i] : 0.f;
+    gt[e] = i < gs ? silu_f(grow[i]) : 0.f;
+    if (gate_first) val[e] *= gt[e];
+    ss = fmaf(val[e], val[e], ss);
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)gs + eps);
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int i = lane + 32 * e;
+    if (i >= gs) continue;
+    const float res = gate_first ? val[e] * inv * w[(base + i) % wn] : val[e] * inv * w[(base + i) % wn] * gt[e];
+    out[(size_t)t * n + base + i] = from_f32<O>(res * out_scale);
+  }
+}
+
 GB_EXPORT int gb_gated_group_norm(const float* y, const float* gate, long long ldgate, const float* w, int wn, void* out,
                                   int out_dtype, int ntok, int n, int gs, float eps, int gate_first, float out_scale,
                                   cudaStream_t stream) {
   if (ntok <= 0) return 0;
   if (gs <= 0 || n % gs || wn <= 0) return GB_ERR_SIZE;
+  if (out_dtype != GB_F32 && out_dtype != GB_BF16) return GB_ERR_DTYPE;
+  if (gs <= 64) {
+    dim3 wgrid(ntok, (n / gs + 7) / 8);
+    if (out_dtype == GB_F32)
+      gb_launch(gated_group_norm_warp_kernel<float>, wgrid, 256, 0, stream, y, gate, ldgate, w, wn, (float*)out, n, gs, eps,
+                gate_first, out_scale);
+    else
+      gb_launch(gated_group_norm_warp_kernel<bf16>, wgrid, 256, 0, stream, y, gate, ldgate, w, wn, (bf16*)out, n, gs, eps,
+                gate_first, out_scale);
+    return gb_launch_status();
+  }
   dim3 grid(ntok, n / gs);
   const int threads = gs <= 32 ? 32 : (gs <= 64 ? 64 : 128);
   if (out_dtype == GB_F32)
@@ -587,6 +632,19 @@ GB_EXPORT int gb_shift_mix(const void* x, int dtype, long long ldx, const float*
 // tanh(z) of the tokens in shared memory (DEC_RC entries of the rank a pass).  Every sum runs over
 // the rank in order with one accumulator, so the result does not depend on the tiling.
 constexpr int DEC_TOK = 8, DEC_RC = 128;
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+  const uint4 a = *(const uint4*)p;
+  const unsigned u[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {      // a bfloat16 is the upper half of the float32 of the same value
+    v[2 * e] = __uint_as_float(u[e] << 16);
+    v[2 * e + 1] = __uint_as_float(u[e] & 0xffff0000u);
+  }
+}
 template <typename T>
 __global__ void __launch_bounds__(128) lowrank_decay_kernel(const float* __restrict__ z, int rank, const T* __restrict__ W,
                                                            const float* __restrict__ base, float* __restrict__ w, int ntok, int C) {
@@ -596,6 +654,7 @@ __global__ void __launch_bounds__(128) lowrank_decay_kernel(const float* __restr
   const int c = blockIdx.x * 128 + threadIdx.x, t0 = blockIdx.y * DEC_TOK;
   const int n = min(DEC_TOK, ntok - t0);
   const T* row = W + (size_t)min(c, C - 1) * rank;
+  const bool vec = rank % 8 == 0 && ((uintptr_t)W & 15) == 0;
   float acc[DEC_TOK];
 #pragma unroll
   for (int tt = 0; tt < DEC_TOK; ++tt) acc[tt] = 0.f;
@@ -607,17 +666,25 @@ __global__ void __launch_bounds__(128) lowrank_decay_kernel(const float* __restr
       th[tt][j] = (tt < n && j < nj) ? tanhf(z[(size_t)(t0 + tt) * rank + j0 + j]) : 0.f;
     }
     __syncthreads();
-    for (int j = 0; j < nj; j += 4) {
-      float wv[4];
+    for (int j = 0; j < nj; j += 8) {
+      float wv[8];
+      if (vec) {         // rows start on 16-byte boundaries and hold a multiple of eight entries
+        load8(row + j0 + j, wv);
+      } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) wv[e] = j + e < nj ? to_f32(row[j0 + j + e]) : 0.f;
+        for (int e = 0; e < 8; ++e) wv[e] = j + e < nj ? to_f32(row[j0 + j + e]) : 0.f;
+      }
 #pragma unroll
       for (int tt = 0; tt < DEC_TOK; ++tt) {
-        const float4 h = *(const float4*)&th[tt][j];
+        const float4 h = *(const float4*)&th[tt][j], g = *(const float4*)&th[tt][j + 4];
         acc[tt] = fmaf(wv[0], h.x, acc[tt]);
         acc[tt] = fmaf(wv[1], h.y, acc[tt]);
         acc[tt] = fmaf(wv[2], h.z, acc[tt]);
         acc[tt] = fmaf(wv[3], h.w, acc[tt]);
+        acc[tt] = fmaf(wv[4], g.x, acc[tt]);
+        acc[tt] = fmaf(wv[5], g.y, acc[tt]);
+        acc[tt] = fmaf(wv[6], g.z, acc[tt]);
+        acc[tt] = fmaf(wv[7], g.w, acc[tt]);
       }
     }
   }
