@@ -71,7 +71,8 @@ def _check_attention(p, w, m, i, layers):
         p.append(f"{w}: {heads} heads are not a multiple of {kv} kv_heads")
     mask = m.get("mask")
     _num(p, w + ".mask", mask, "size")
-    _num(p, w + ".mask", mask, "keep_first", allow_zero=True)
+    if isinstance(mask, dict) and "keep_first" in mask:      # absent: no first token is kept
+        _num(p, w + ".mask", mask, "keep_first", allow_zero=True)
     rot = m.get("rot")
     _num(p, w + ".rot", rot, "base", float)
     dims = _num(p, w + ".rot", rot, "dims", allow_zero=True)
@@ -192,7 +193,7 @@ def _attention_spec(cfg, m, prefix, shared: bool) -> PartSpec:
     names = {k: prefix + k for k in (("q", "k", "v", "o", "sink") if has_kv else ("q", "o", "sink"))}
     return PartSpec("capped_attention", {
         "hidden_size": cfg.width, "heads": int(m["heads"]), "kv_heads": int(m["kv_heads"]), "dim": int(m["dim"]),
-        "vdim": int(m["vdim"]), "window": int(m["mask"]["size"]), "keep_first": int(m["mask"]["keep_first"]),
+        "vdim": int(m["vdim"]), "window": int(m["mask"]["size"]), "keep_first": int(m["mask"].get("keep_first", 0)),
         "sink": True, "scale": float(m["scale"]), "position": position, "has_kv": has_kv,
         # a cache that several layers read keeps every page: each reader masks for itself
         "ring": not shared}, names)
