@@ -931,6 +931,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     if (lane == 0) {
       uint32_t it = 0, i = 0;
       bool ok = true;
+      // which tiles are used is written by a kernel before this one: it must have ended before the
+      // list is read, or this thread would skip other tiles than the producer and wait for a stage
+      // that is never filled
+      if (grp.tile_expert) pdl_wait_prior();
       for (TileWalk w(tiles, kb_total, split); w.more() && ok; w.next(), ++i) {
         if (grp.tile_expert) {                         // a tile no group uses: not counted, as in the other roles
           int m0, n0;

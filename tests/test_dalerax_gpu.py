@@ -539,6 +539,34 @@ def test_sizes_the_tensor_cores_do_not_take(dtype, tmp_path_factory):
     assert runner.cache.pages_held() == 0
 
 
+def test_routed_layers_of_unequal_shapes_in_long_prompts(tmp_path_factory):
+    """Three routed feed-forwards with other expert counts and other numbers chosen, in prompts of
+    more than 256 tokens on the tensor cores: the list of token tiles that the experts use differs
+    from layer to layer, and every role of the grouped product has to read this layer's list, not
+    what the layer before left there.  Several prompts one after the other, the status of every
+    bounded wait checked, the logits against the plain implementation."""
+    from gemmars_b200 import kernels
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    from tiny_configs import _dalerax_attention, _dalerax_moe
+    raw = {"architecture": "Dalerax", "vocab": 150, "width": 320, "max_positions": 600, "logit_scale": 0.7,
+           "embedding": {"scale": 4.0}, "norm": {"eps": 1e-6},
+           "layers": [{"type": "wkv", "mixer": {"heads": 4, "dim": 16, "rank": 16}, "mlp": _dalerax_moe(14, 1, 48, 128)},
+                      {"type": "attention", "mixer": _dalerax_attention(6, 2, 48, 32, 0.125, 129, 9, 1e6, 48), "mlp": _dalerax_moe(7, 4, 48, 32)},
+                      {"type": "wkv", "mixer": {"heads": 1, "dim": 16, "rank": 16}, "mlp": _dalerax_moe(2, 2, 48, 0)}]}
+    folder = _sharp_folder(tmp_path_factory, raw, seed=7, factor=3.0)
+    cfg, w = plain.load_folder(folder)
+    rng = np.random.default_rng(7)
+    runner = Runner(build_model(folder, dtype="bfloat16"), max_tokens=16 * PAGE, max_batch=2)
+    for n in (301, 261, 496, 260, 301):
+        toks = rng.integers(0, raw["vocab"], n).tolist()
+        slot = runner.open()
+        got = runner.step([StepItem(slot, toks, [n - 2, n - 1])]).cpu().numpy()
+        kernels.check_status()
+        runner.close(slot)
+        want = plain.forward(cfg, w, toks)[-2:]
+        assert np.abs(got - want).max() <= 2 * TOL_BF16 * np.abs(want).max(), f"a prompt of {n} tokens"
+
+
 def test_greedy_generation_through_the_engine(models):
     from gemmars_b200 import Engine
     folder, cfg, w, reqs, _ = models["A"]
