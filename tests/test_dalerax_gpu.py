@@ -190,7 +190,7 @@ SCALING = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64.0}
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,groups,dim,vdim,rot,window,keep",
                          [(4, 2, 32, 16, 16, 20, 3), (3, 3, 16, 24, 0, 7, 0), (8, 4, 64, 128, 32, 130, 70), (2, 1, 128, 128, 128, 200, 5),
-                          (6, 2, 64, 64, 64, 64, 1), (2, 2, 48, 80, 8, 33, 65), (5, 1, 20, 12, 4, 17, 2), (4, 1, 64, 64, 32, 400, 4),
+                          (9, 3, 64, 64, 32, 64, 1), (2, 2, 48, 80, 8, 33, 65), (5, 1, 20, 12, 4, 17, 2), (4, 1, 64, 64, 32, 400, 4),
                           # more query heads a kv head than a tensor-core block takes at once: 6, 7 and 18
                           (12, 2, 64, 64, 32, 50, 2), (7, 1, 64, 64, 16, 90, 0), (18, 1, 64, 64, 64, 40, 3)])
 def test_sink_attention_finds_planted_keys(dtype, heads, groups, dim, vdim, rot, window, keep):
