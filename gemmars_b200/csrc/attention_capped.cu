@@ -3,9 +3,14 @@
 // any precision and size; the arithmetic for one (token, head) depends on its position and the
 // cache alone, so prompts, parts of prompts and single tokens give the same bits.
 //
-//   gb_filter_rope_cache:  u [T, q | k | v] -> filter over time -> rotation of the first `rot`
-//                          dims of every q and k head (dim i pairs with i + rot/2; angle
-//                          float(pos) * inv_freq[i], float32) -> q rows, keys and values into pages
+//   gb_filter_rope_cache:  u [T, q | k | v] -> filter over time -> RMS norm of every q and k head
+//                          with a weight over its dims (when weights are given) -> rotation of the
+//                          first `rot` dims of every q and k head (dim i pairs with i + rot/2; angle
+//                          float(pos) * inv_freq[i], float32; cosines and sines times `rot_mag`) ->
+//                          q times 1 + qt_coef ln(floor((pos + 1) / qt_every) + 1) (when qt_every)
+//                          -> q rows, keys and values into pages.  With `v_from_k` the rows hold
+//                          q | k only and a value head is its key head as projected and filtered,
+//                          before norm and rotation
 //   gb_attention_capped:   score = (q . k) * scale; score <- cap * tanh(score / cap) when cap > 0;
 //                          keys lo..p with lo = max(0, p + 1 - window), and with `keep_first` the
 //                          keys 0..keep_first-1 as well, wherever the window stands; softmax, whose
@@ -45,13 +50,15 @@ __global__ void __launch_bounds__(128) filter_rope_cache_kernel(
     const float* __restrict__ inv_freq, int rot, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
     const int* __restrict__ seq_slot, const int* __restrict__ cu, const int* __restrict__ page_table, int table_width,
     int page_size, T* __restrict__ q_out, long long ldq, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int D,
-    int Vd) {
+    int Vd, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float norm_eps, float rot_mag, float qt_coef,
+    int qt_every, int v_from_k) {
   __shared__ float vals[MAX_HEAD], cs[MAX_HEAD];   // cs: cos[rot / 2], then sin[rot / 2]
+  __shared__ float scratch[33];
   pdl_release_next();
   pdl_wait_prior();
   const int t = blockIdx.x, hh = blockIdx.y, b = tok_seq[t], pos = tok_pos[t], slot = seq_slot[b];
   const int row0 = cu[b], local = t - row0, half = rot / 2;
-  const int C = (H + G) * D + G * Vd;
+  const int C = (H + G) * D + (v_from_k ? 0 : G * Vd);
   const float* hist = K > 1 ? state + (size_t)slot * (K - 1) * C : nullptr;
   const int page = page_table ? page_table[(size_t)slot * table_width + (pos / page_size) % table_width] : 0;
   const int off = pos % page_size;
@@ -59,19 +66,33 @@ __global__ void __launch_bounds__(128) filter_rope_cache_kernel(
     if (!vcache) return;
     const int g = hh - H - G;
     for (int d = threadIdx.x; d < Vd; d += blockDim.x) {
-      const int c = (H + G) * D + g * Vd + d;
+      const int c = (v_from_k ? H * D : (H + G) * D) + g * Vd + d;
       const float val = K > 1 ? filtered(u, ldu, row0, local, hist, taps, C, c, K) : to_f32(u[(size_t)t * ldu + c]) * (K == 1 ? taps[c] : 1.f);
       vcache[(((size_t)page * G + g) * Vd + d) * page_size + off] = from_f32<T>(val);
     }
     return;
   }
   if (hh >= H && !kcache) return;
+  const float* norm_w = hh < H ? q_norm : k_norm;
+  float ss = 0.f;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     const int e = hh * D + i;
-    vals[i] = K > 1 ? filtered(u, ldu, row0, local, hist, taps, C, e, K) : to_f32(u[(size_t)t * ldu + e]) * (K == 1 ? taps[e] : 1.f);
-    if (i < half) sincosf((float)pos * inv_freq[i], &cs[half + i], &cs[i]);
+    const float x = K > 1 ? filtered(u, ldu, row0, local, hist, taps, C, e, K) : to_f32(u[(size_t)t * ldu + e]) * (K == 1 ? taps[e] : 1.f);
+    vals[i] = x;
+    ss = fmaf(x, x, ss);
+    if (i < half) {
+      float sn, cn;
+      sincosf((float)pos * inv_freq[i], &sn, &cn);
+      cs[half + i] = sn * rot_mag;
+      cs[i] = cn * rot_mag;
+    }
+  }
+  if (norm_w) {            // the head divided by its root mean square, times the weight of each dim
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)D + norm_eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) vals[i] = vals[i] * inv * norm_w[i];
   }
   __syncthreads();
+  const float temper = (hh < H && qt_every > 0) ? 1.0f + qt_coef * logf((float)((pos + 1) / qt_every + 1)) : 1.0f;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float val = vals[i];
     if (i < rot) {
@@ -79,34 +100,47 @@ __global__ void __launch_bounds__(128) filter_rope_cache_kernel(
       const int j = i < half ? i : i - half;
       val = i < half ? val * cs[j] - vals[i + half] * cs[half + j] : val * cs[j] + vals[i - half] * cs[half + j];
     }
-    if (hh < H) q_out[(size_t)t * ldq + hh * D + i] = from_f32<T>(val);
+    if (hh < H) q_out[(size_t)t * ldq + hh * D + i] = from_f32<T>(val * temper);
     else kcache[(((size_t)page * G + (hh - H)) * page_size + off) * D + i] = from_f32<T>(val);
   }
 }
 
 // taps: [(H + G) D + G Vd, K] float32 (K = 0: no filter); state: [slots, K - 1, channels] float32.
 // G = 0: the rows hold queries only (a layer that reads another layer's keys and values).
+// q_norm, k_norm: float32 [D] or null; v_from_k needs Vd == D.
+GB_EXPORT int gb_filter_rope_cache_ext(const void* u, int dtype, long long ldu, const float* taps, const float* state, int K,
+                                       const float* inv_freq, int rot, const int* tok_pos, const int* tok_seq,
+                                       const int* seq_slot, const int* cu, const int* page_table, int table_width,
+                                       int page_size, void* q_out, long long ldq, void* kcache, void* vcache, int ntok, int H,
+                                       int G, int D, int Vd, const float* q_norm, const float* k_norm, float norm_eps,
+                                       float rot_mag, float qt_coef, int qt_every, int v_from_k, cudaStream_t stream) {
+  if (ntok <= 0) return 0;
+  if (K < 0 || K > MAX_TAPS || rot < 0 || rot > D || rot % 2 || H <= 0 || G < 0 || D <= 0 || D > MAX_HEAD || Vd <= 0)
+    return GB_ERR_SIZE;
+  if (v_from_k && (Vd != D || K > 1)) return GB_ERR_SIZE;
+  if ((K > 0 && !taps) || (K > 1 && !state) || (rot > 0 && !inv_freq) || qt_every < 0) return GB_ERR_ARG;
+  const dim3 grid(ntok, H + 2 * G);
+  if (dtype == GB_F32)
+    gb_launch(filter_rope_cache_kernel<float>, grid, 128, 0, stream, (const float*)u, ldu, taps, state, K, inv_freq, rot,
+              tok_pos, tok_seq, seq_slot, cu, page_table, table_width, page_size, (float*)q_out, ldq, (float*)kcache,
+              (float*)vcache, H, G, D, Vd, q_norm, k_norm, norm_eps, rot_mag, qt_coef, qt_every, v_from_k);
+  else if (dtype == GB_BF16)
+    gb_launch(filter_rope_cache_kernel<bf16>, grid, 128, 0, stream, (const bf16*)u, ldu, taps, state, K, inv_freq, rot,
+              tok_pos, tok_seq, seq_slot, cu, page_table, table_width, page_size, (bf16*)q_out, ldq, (bf16*)kcache,
+              (bf16*)vcache, H, G, D, Vd, q_norm, k_norm, norm_eps, rot_mag, qt_coef, qt_every, v_from_k);
+  else
+    return GB_ERR_DTYPE;
+  return gb_launch_status();
+}
+
 GB_EXPORT int gb_filter_rope_cache(const void* u, int dtype, long long ldu, const float* taps, const float* state, int K,
                                    const float* inv_freq, int rot, const int* tok_pos, const int* tok_seq, const int* seq_slot,
                                    const int* cu, const int* page_table, int table_width, int page_size, void* q_out,
                                    long long ldq, void* kcache, void* vcache, int ntok, int H, int G, int D, int Vd,
                                    cudaStream_t stream) {
-  if (ntok <= 0) return 0;
-  if (K < 0 || K > MAX_TAPS || rot < 0 || rot > D || rot % 2 || H <= 0 || G < 0 || D <= 0 || D > MAX_HEAD || Vd <= 0)
-    return GB_ERR_SIZE;
-  if ((K > 0 && !taps) || (K > 1 && !state) || (rot > 0 && !inv_freq)) return GB_ERR_ARG;
-  const dim3 grid(ntok, H + 2 * G);
-  if (dtype == GB_F32)
-    gb_launch(filter_rope_cache_kernel<float>, grid, 128, 0, stream, (const float*)u, ldu, taps, state, K, inv_freq, rot,
-              tok_pos, tok_seq, seq_slot, cu, page_table, table_width, page_size, (float*)q_out, ldq, (float*)kcache,
-              (float*)vcache, H, G, D, Vd);
-  else if (dtype == GB_BF16)
-    gb_launch(filter_rope_cache_kernel<bf16>, grid, 128, 0, stream, (const bf16*)u, ldu, taps, state, K, inv_freq, rot,
-              tok_pos, tok_seq, seq_slot, cu, page_table, table_width, page_size, (bf16*)q_out, ldq, (bf16*)kcache,
-              (bf16*)vcache, H, G, D, Vd);
-  else
-    return GB_ERR_DTYPE;
-  return gb_launch_status();
+  return gb_filter_rope_cache_ext(u, dtype, ldu, taps, state, K, inv_freq, rot, tok_pos, tok_seq, seq_slot, cu, page_table,
+                                  table_width, page_size, q_out, ldq, kcache, vcache, ntok, H, G, D, Vd, nullptr, nullptr, 0.f,
+                                  1.f, 0.f, 0, 0, stream);
 }
 
 // One block per (token, query head); online softmax over chunks of 128 keys: first the kept keys

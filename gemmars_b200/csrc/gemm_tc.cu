@@ -811,13 +811,23 @@ constexpr int PERSISTENT_QKV_THREADS = 320, QKV_STAGING_BYTES = 65 * 1024;   // 
 // group; tile_expert[m tile] names it (-1: a tile no group uses, which every role skips) and the
 // tile's rows of W are the group's (W stacks the groups' matrices, rows_per_expert each).  The gated
 // mode then applies g = min(g, limit), u = clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + shift)
-// when limit > 0, and multiplies row r of the result by row_scale[r].
+// when limit > 0, and multiplies row r of the result by row_scale[r].  `act` 1 (bfloat16 results of
+// a product without a gate): the exact (erf) GELU of every result, then the row's scale.
 struct Grouped {
   const int* tile_expert = nullptr;
   const float* row_scale = nullptr;
   int rows_per_expert = 0;
   float limit = 0.f, alpha = 0.f, shift = 0.f;
+  int act = 0;
 };
+__device__ __forceinline__ void gelu_rows(uint32_t (&v)[16], const float* row_scale, int row, int M) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float x = __uint_as_float(v[j]);
+    const float sc = row_scale ? (row + j < M ? row_scale[row + j] : 0.f) : 1.f;
+    v[j] = __float_as_uint(0.5f * x * (1.0f + erff(x * 0.70710678118654752f)) * sc);
+  }
+}
 __device__ __forceinline__ float clamped_gate(float g, float u, const Grouped& grp) {
   g = fminf(g, grp.limit);
   u = fminf(fmaxf(u, -grp.limit), grp.limit);
@@ -1066,11 +1076,17 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             x[16 + j] = __uint_as_float(v2[j]) + bv;
           }
           qkv_prompt_round<MODE, SLOT>(tail, x, n0 / BM, quarter, lane, m0 + c, M, tail.nh * BM, tail_shared, tile_out, 1 + group);
-        } else if (y_tma) {
-          tile_out.send(v, v2, both, bv, lane, n0 + warp * 32, m0 + c, N);
         } else {
-          store_direct<MODE>(y, ldy, v, bv, m0 + c, M, n, N);
-          if (both) store_direct<MODE>(y, ldy, v2, bv, m0 + c + 16, M, n, N);
+          if (MODE == EPI_STORE_BF16 && grp.act == 1) {
+            gelu_rows(v, grp.row_scale, m0 + c, M);
+            if (both) gelu_rows(v2, grp.row_scale, m0 + c + 16, M);
+          }
+          if (y_tma) {
+            tile_out.send(v, v2, both, bv, lane, n0 + warp * 32, m0 + c, N);
+          } else {
+            store_direct<MODE>(y, ldy, v, bv, m0 + c, M, n, N);
+            if (both) store_direct<MODE>(y, ldy, v2, bv, m0 + c + 16, M, n, N);
+          }
         }
       }
       tc_fence_before();
@@ -1404,7 +1420,8 @@ GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* b
 // group after the other, each group starting at a multiple of bn rows (M counts the padding);
 // w stacks `experts` matrices of N rows (2 N gated: gate rows, then up rows); tile_expert [M / bn].
 // mode 1: y float32 [M, N] = x W_g^T; mode 3: y bfloat16 [M, N] = row_scale * act(gate, up), act the
-// clamped form when limit > 0.  bn: 128 or 256.
+// clamped form when limit > 0; mode 0: y bfloat16 [M, N] = row_scale * gelu(x W_g^T) (erf form; no
+// gate rows in w).  bn: 128 or 256.
 GB_EXPORT int gb_gemm_tc_grouped(const void* x, const void* w, void* y, int mode, int M, int N, int K, long long ldx,
                                  long long ldy, int bn, int ctas, int experts, const int* tile_expert, const float* row_scale,
                                  float limit, float alpha, float shift, cudaStream_t stream) {
@@ -1412,12 +1429,13 @@ GB_EXPORT int gb_gemm_tc_grouped(const void* x, const void* w, void* y, int mode
   if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return GB_ERR_SIZE;
   if ((bn != 128 && bn != 256) || M % bn || !tile_expert) return GB_ERR_SIZE;
   const bool gated = mode == EPI_SWIGLU_BF16;
-  if (!gated && mode != EPI_STORE_F32) return GB_ERR_ARG;
+  if (!gated && mode != EPI_STORE_F32 && mode != EPI_STORE_BF16) return GB_ERR_ARG;
   Grouped grp;
   grp.tile_expert = tile_expert;
-  grp.row_scale = gated ? row_scale : nullptr;
+  grp.row_scale = (gated || mode == EPI_STORE_BF16) ? row_scale : nullptr;
   grp.rows_per_expert = N * (gated ? 2 : 1);
   grp.limit = limit; grp.alpha = alpha; grp.shift = shift;
+  grp.act = mode == EPI_STORE_BF16 ? 1 : 0;
   CUtensorMap mw, mx;
   if (!tensor_map(&mw, w, (uint64_t)experts * grp.rows_per_expert, (uint64_t)K, (uint64_t)K * 2, gated ? BM / 2 : BM)) return GB_ERR_ARG;
   if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
@@ -1425,6 +1443,10 @@ GB_EXPORT int gb_gemm_tc_grouped(const void* x, const void* w, void* y, int mode
   if (gated) {
     if (bn > 128) return launch_persistent<256, 4, EPI_SWIGLU_BF16>(mw, mx, my, nullptr, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, nullptr, grp);
     return launch_persistent<128, 6, EPI_SWIGLU_BF16>(mw, mx, my, nullptr, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, nullptr, grp);
+  }
+  if (mode == EPI_STORE_BF16) {
+    if (bn > 128) return launch_persistent<256, 4, EPI_STORE_BF16>(mw, mx, my, nullptr, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, nullptr, grp);
+    return launch_persistent<128, 6, EPI_STORE_BF16>(mw, mx, my, nullptr, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, nullptr, grp);
   }
   if (bn > 128) return launch_persistent<256, 4, EPI_STORE_F32>(mw, mx, my, nullptr, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, nullptr, grp);
   return launch_persistent<128, 6, EPI_STORE_F32>(mw, mx, my, nullptr, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, nullptr, grp);

@@ -34,7 +34,9 @@ struct GroupedArgs {
   const int* offsets;                        // [groups + 1], or null: every group has `rows` rows
   int groups, rows, N, K;
   float limit, alpha, shift;                 // gated: g = min(g, limit), u = clamp(u, +-limit), g * sigmoid(alpha g) * (u + shift)
+  int act;                                   // plain mode: 1 = the exact (erf) GELU of every result before the scale
 };
+__device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
 
 __device__ __forceinline__ void cp_async16_or_zero(void* smem, const void* gmem, bool valid) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -177,7 +179,9 @@ __global__ void __launch_bounds__(256, 2) grouped_gemm_kernel(GroupedArgs p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int col = n0 + wn * 32 + j * 8 + 2 * cq;
-          const float x = acc[i][j][2 * half] * sc, y = acc[i][j][2 * half + 1] * sc;
+          float x = acc[i][j][2 * half], y = acc[i][j][2 * half + 1];
+          if (p.act == 1) { x = gelu_erf_f(x); y = gelu_erf_f(y); }
+          x *= sc; y *= sc;
           if (col + 1 < p.N && ((uintptr_t)(dst + col) & (2 * sizeof(TO) - 1)) == 0) {
             store2(dst + col, x, y);
           } else {
@@ -317,8 +321,8 @@ int launch_grouped(const GroupedArgs& p, int row_tiles, cudaStream_t stream) {
 
 }  // namespace
 
-// The general form; see GroupedArgs.  out_f32: C is float32 (else bfloat16); gated: W_g has 2N rows
-// and C = act(gate, up) in bfloat16.  max_rows: an upper bound of the rows over all groups (the
+// The general form; see GroupedArgs.  out_f32: C is float32 (else bfloat16); gated 1: W_g has 2N rows
+// and C = act(gate, up) in bfloat16; gated 2: W_g has N rows and C = gelu(A W_g^T) (erf form).  max_rows: an upper bound of the rows over all groups (the
 // grid is sized by it when the counts live on the device).
 GB_EXPORT int gb_grouped_gemm(const void* a, long long lda, long long a_gstride, const int* a_rows, int a_div,
                               const void* w, long long w_gstride, void* c, long long ldc, long long c_gstride,
@@ -327,11 +331,12 @@ GB_EXPORT int gb_grouped_gemm(const void* a, long long lda, long long a_gstride,
                               float limit, float alpha, float shift, cudaStream_t stream) {
   if (groups <= 0 || N <= 0 || max_rows <= 0) return 0;
   if (K <= 0 || K % 8 || lda % 8 || a_gstride % 8 || w_gstride % 8 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return GB_ERR_SIZE;
-  if (gated && out_f32) return GB_ERR_DTYPE;
+  if (gated == 1 && out_f32) return GB_ERR_DTYPE;
+  if (gated < 0 || gated > 2) return GB_ERR_ARG;
   GroupedArgs p{(const bf16*)a, lda, a_gstride, a_rows, a_div > 0 ? a_div : 1, (const bf16*)w, w_gstride, c, ldc, c_gstride,
-                scale, scale_rows, s_rstride, s_gstride, offsets, groups, rows, N, K, limit, alpha, shift};
+                scale, scale_rows, s_rstride, s_gstride, offsets, groups, rows, N, K, limit, alpha, shift, gated == 2 ? 1 : 0};
   const int row_tiles = offsets ? (max_rows + BM - 1) / BM + groups : groups * ((rows + BM - 1) / BM);
-  if (gated) return launch_grouped<MODE_GATED, bf16>(p, row_tiles, stream);
+  if (gated == 1) return launch_grouped<MODE_GATED, bf16>(p, row_tiles, stream);
   if (out_f32) return launch_grouped<MODE_PLAIN, float>(p, row_tiles, stream);
   return launch_grouped<MODE_PLAIN, bf16>(p, row_tiles, stream);
 }

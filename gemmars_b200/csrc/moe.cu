@@ -6,6 +6,10 @@
 //              y = g * sigmoid(alpha g) * (u + shift);  out = down y
 //   residual[t] += sum over chosen of weight * expert_e(h[t])  +  sigmoid(sg . h[t]) * shared(h[t])
 //
+// Two more forms for designs that ask for them: `all_softmax` (the weights are the chosen experts'
+// shares of the softmax over ALL experts, not renormalized), and experts without a gate
+// (`gated` 0: y = gelu(up h) with the exact, erf form; out = down y; w_gu then is [E, ff, width]).
+//
 // The router's logits are a product like any other (the part computes them in float32); this unit
 // picks the experts from them and runs the experts token-major: a block owns one (token, chosen
 // expert) pair and a run of the expert's features, so the kernels need nothing from the host about
@@ -71,7 +75,7 @@ template <typename T> __device__ __forceinline__ bool rows_vectorize(const T* ba
 __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__ zin, long long ldz,
                                                        const float* __restrict__ bias, int* __restrict__ idx,
                                                        float* __restrict__ wts, float* __restrict__ sg, int ntok, int E,
-                                                       int top, int has_gate) {
+                                                       int top, int has_gate, int all_softmax) {
   extern __shared__ float smem[];
   pdl_release_next();
   pdl_wait_prior();
@@ -82,6 +86,14 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
   for (int e = lane; e < E; e += 32) z[e] = zin[(size_t)t * ldz + e] + (bias ? bias[e] : 0.f);
   if (has_gate && lane == 0) sg[t] = 1.0f / (1.0f + expf(-zin[(size_t)t * ldz + E]));
   __syncwarp();
+  float total = 0.f;               // all_softmax: the sum of exp(z - max) over every expert, in index order per lane
+  if (all_softmax) {
+    float top1 = -INFINITY;
+    for (int e = lane; e < E; e += 32) top1 = fmaxf(top1, z[e]);
+    top1 = warp_max(top1);
+    for (int e = lane; e < E; e += 32) total += expf(z[e] - top1);
+    total = warp_sum(total);
+  }
   float mine = 0.f, first = 0.f;   // lane k keeps the k-th chosen logit
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
@@ -106,7 +118,7 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
   }
   const float e = lane < top ? expf(mine - first) : 0.f;
   const float sum = warp_sum(e);
-  if (lane < top) wts[(size_t)t * top + lane] = e / sum;
+  if (lane < top) wts[(size_t)t * top + lane] = e / (all_softmax ? total : sum);
 }
 
 // ---- gate and up of one (token, slot): FEATS features a block, a warp per feature in turn
@@ -142,6 +154,36 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T* __restrict__ 
       u = fminf(fmaxf(u, -lim), lim);
       const float a = g / (1.0f + expf(-alpha * g)) * (u + shift);
       y[((size_t)t * slots + s) * ffmax + f] = from_f32<T>(a);
+    }
+  }
+}
+
+// ---- the same for experts without a gate: y = gelu(up h) (erf form), two features a warp at a time
+__device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_up_kernel(const T* __restrict__ h, long long ldh, const int* __restrict__ idx,
+                                                     const T* __restrict__ w_up, T* __restrict__ y, int width, int ff, int top) {
+  extern __shared__ float xs[];   // [width]
+  pdl_release_next();
+  pdl_wait_prior();
+  const int t = blockIdx.x / top, s = blockIdx.x % top;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int f0 = blockIdx.y * FEATS;
+  if (f0 >= ff) return;
+  const T* W = w_up + (size_t)idx[(size_t)t * top + s] * ff * width;
+  for (int i = tid; i < width; i += 256) xs[i] = to_f32(h[(size_t)t * ldh + i]);
+  __syncthreads();
+  const bool vec = rows_vectorize(W, width);
+  for (int f = f0 + warp * 2; f < min(ff, f0 + FEATS); f += 16) {
+    float a, b;
+    const bool two = f + 1 < ff;
+    lane_dot2(W + (size_t)f * width, W + (size_t)(two ? f + 1 : f) * width, xs, width, lane, vec, a, b);
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (lane == 0) {
+      y[((size_t)t * top + s) * ff + f] = from_f32<T>(gelu_erf_f(a));
+      if (two) y[((size_t)t * top + s) * ff + f + 1] = from_f32<T>(gelu_erf_f(b));
     }
   }
 }
@@ -192,13 +234,18 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const float* __restrict__ 
   }
 }
 
-GB_EXPORT int gb_moe_topk(const float* z, long long ldz, const float* bias, int* idx, float* wts, float* sg, int ntok,
-                          int E, int top, int has_gate, cudaStream_t stream) {
+GB_EXPORT int gb_moe_topk_mode(const float* z, long long ldz, const float* bias, int* idx, float* wts, float* sg, int ntok,
+                               int E, int top, int has_gate, int all_softmax, cudaStream_t stream) {
   if (ntok <= 0) return 0;
   if (E <= 0 || top <= 0 || top > 32 || top > E || E > 2048) return GB_ERR_SIZE;
   gb_launch(moe_topk_kernel, dim3((ntok + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), stream, z, ldz, bias, idx, wts, sg,
-            ntok, E, top, has_gate);
+            ntok, E, top, has_gate, all_softmax);
   return gb_launch_status();
+}
+
+GB_EXPORT int gb_moe_topk(const float* z, long long ldz, const float* bias, int* idx, float* wts, float* sg, int ntok,
+                          int E, int top, int has_gate, cudaStream_t stream) {
+  return gb_moe_topk_mode(z, ldz, bias, idx, wts, sg, ntok, E, top, has_gate, 0, stream);
 }
 
 // w_gu: [E, 2 ff, width] (an expert's gate rows, then its up rows); ws_gu: [2 ffs, width] or null;
@@ -218,6 +265,25 @@ GB_EXPORT int gb_moe_gate_up(const void* h, long long ldh, int dtype, const int*
   else if (dtype == GB_BF16)
     gb_launch(moe_gate_up_kernel<bf16>, grid, dim3(256), smem, stream, (const bf16*)h, ldh, idx, (const bf16*)w_gu,
               (const bf16*)ws_gu, (bf16*)y, width, ff, ffs, ffmax, top, slots, limit, limit_s, alpha, shift);
+  else
+    return GB_ERR_DTYPE;
+  return gb_launch_status();
+}
+
+// Experts without a gate: w_up [E, ff, width]; y: [ntok, top, ff] = gelu(up h) of every chosen expert.
+GB_EXPORT int gb_moe_up(const void* h, long long ldh, int dtype, const int* idx, const void* w_up, void* y, int ntok, int width,
+                        int ff, int top, cudaStream_t stream) {
+  if (ntok <= 0) return 0;
+  if (width <= 0 || ff <= 0 || top <= 0) return GB_ERR_SIZE;
+  const size_t smem = (size_t)width * sizeof(float);
+  if (smem > 48 * 1024) return GB_ERR_SIZE;
+  dim3 grid(ntok * top, (ff + FEATS - 1) / FEATS);
+  if (dtype == GB_F32)
+    gb_launch(moe_up_kernel<float>, grid, dim3(256), smem, stream, (const float*)h, ldh, idx, (const float*)w_up, (float*)y,
+              width, ff, top);
+  else if (dtype == GB_BF16)
+    gb_launch(moe_up_kernel<bf16>, grid, dim3(256), smem, stream, (const bf16*)h, ldh, idx, (const bf16*)w_up, (bf16*)y, width,
+              ff, top);
   else
     return GB_ERR_DTYPE;
   return gb_launch_status();

@@ -217,19 +217,23 @@ __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.com
 template <int N>
 __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int P>
+// CH: the decay is a vector per head, one number per key channel, given as it is (``a_logit`` then
+// holds the decays, rows of ``lda`` floats, head h at h * D): row d of S is multiplied by g_d before
+// the token's read and write.  A_log and dt_bias are not read.
+template <int P, bool CH>
 __global__ void __launch_bounds__(32 * P) delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k,
                                                            const float* __restrict__ v, long long ld,
                                                            const float* __restrict__ beta_logit, const float* __restrict__ a_logit,
-                                                           long long ldg, const float* __restrict__ A_log,
+                                                           long long ldg, long long lda, const float* __restrict__ A_log,
                                                            const float* __restrict__ dt_bias, float* __restrict__ state,
                                                            const int* __restrict__ cu, const int* __restrict__ seq_slot,
                                                            float* __restrict__ y, int H, int G, int D, int V, float qscale) {
   constexpr int DP = P * SLICE;
-  __shared__ __align__(16) float kq[2][GROUP][2][padded_size(P)];   // [buffer][token][k | q][dims, padded]
-  __shared__ float vs[2][GROUP][32], gates[2][GROUP][2];
-  __shared__ float pre[GROUP][4];                       // per token: decay, 1/|k|, beta, (k^ . q^); then decay * qscale/|q|
-  __shared__ float pre_q[GROUP];
+  constexpr int GRP = (CH && P == 8) ? GROUP / 2 : GROUP;   // tokens a group: what 48 KB of shared memory hold
+  __shared__ __align__(16) float kq[2][GRP][CH ? 3 : 2][padded_size(P)];   // [buffer][token][k | q (| decay)][dims, padded]
+  __shared__ float vs[2][GRP][32], gates[2][GRP][2];
+  __shared__ float pre[GRP][4];                       // per token: decay, 1/|k|, beta, (k^ . q^); then decay * qscale/|q|
+  __shared__ float pre_q[GRP];
   pdl_wait_prior();
   const int b = blockIdx.x, head = blockIdx.y, g = head / (H / G), tid = threadIdx.x;
   const int col = blockIdx.z * 32 + tid / P, part = tid % P, lane = tid & 31, warp = tid >> 5;
@@ -242,34 +246,36 @@ __global__ void __launch_bounds__(32 * P) delta_rule_kernel(const float* __restr
     const float4 s4 = live ? Sg[((size_t)r * V + col) * P + part] : make_float4(0.f, 0.f, 0.f, 0.f);
     S[4 * r] = s4.x; S[4 * r + 1] = s4.y; S[4 * r + 2] = s4.z; S[4 * r + 3] = s4.w;
   }
-  const float rate = expf(A_log[head]), dtb = dt_bias[head];
+  const float rate = CH ? 0.f : expf(A_log[head]), dtb = CH ? 0.f : dt_bias[head];
   if (tid >= D)      // the dims beyond the head's are zeros, written once
-    for (int j = 0; j < 2 * GROUP; ++j) kq[j / GROUP][j % GROUP][0][padded(tid)] = kq[j / GROUP][j % GROUP][1][padded(tid)] = 0.f;
+    for (int j = 0; j < 2 * GRP; ++j)
+      for (int a = 0; a < (CH ? 3 : 2); ++a) kq[j / GRP][j % GRP][a][padded(tid)] = 0.f;
   // every thread brings one dim of k and of q of every token of a group
   auto bring = [&](int first, int buf) {
-    for (int j = 0; j < GROUP && first + j < t1; ++j) {
+    for (int j = 0; j < GRP && first + j < t1; ++j) {
       const size_t t = first + j;
       if (tid < D) {
         copy_async4(&kq[buf][j][0][padded(tid)], k + t * ld + g * D + tid);
         copy_async4(&kq[buf][j][1][padded(tid)], q + t * ld + g * D + tid);
+        if (CH) copy_async4(&kq[buf][j][2][padded(tid)], a_logit + t * lda + head * D + tid);
       }
       if (live && part == 0) copy_async4(&vs[buf][j][tid / P], v + t * ld + head * V + col);
       if (tid == 0) copy_async4(&gates[buf][j][0], beta_logit + t * ldg + head);
-      if (tid == 1) copy_async4(&gates[buf][j][1], a_logit + t * ldg + head);
+      if (!CH && tid == 1) copy_async4(&gates[buf][j][1], a_logit + t * lda + head);
     }
     copy_async_commit();
   };
   bring(t0, 0);
-  for (int first = t0; first < t1; first += GROUP) {
-    const int buf = ((first - t0) / GROUP) & 1;
-    if (first + GROUP < t1) {
-      bring(first + GROUP, buf ^ 1);
+  for (int first = t0; first < t1; first += GRP) {
+    const int buf = ((first - t0) / GRP) & 1;
+    if (first + GRP < t1) {
+      bring(first + GRP, buf ^ 1);
       copy_async_wait<1>();
     } else {
       copy_async_wait<0>();
     }
     __syncthreads();
-    const int n = min(GROUP, t1 - first);
+    const int n = min(GRP, t1 - first);
     for (int j = warp; j < n; j += P) {       // a token a warp: what the state has no part in
       float kk = 0.f, qq = 0.f, kdq = 0.f;
       for (int i = lane; i < DP; i += 32) {
@@ -279,7 +285,7 @@ __global__ void __launch_bounds__(32 * P) delta_rule_kernel(const float* __restr
       kk = warp_sum(kk); qq = warp_sum(qq); kdq = warp_sum(kdq);
       if (lane == 0) {
         const float inv_k = 1.0f / sqrtf(kk + 1e-6f), inv_q = qscale / sqrtf(qq + 1e-6f);
-        const float decay = expf(-rate * softplus_f(gates[buf][j][1] + dtb));
+        const float decay = CH ? 1.0f : expf(-rate * softplus_f(gates[buf][j][1] + dtb));
         pre[j][0] = decay; pre[j][1] = inv_k; pre[j][2] = sigmoid_f(gates[buf][j][0]); pre[j][3] = kdq * inv_k * inv_q;
         pre_q[j] = decay * inv_q;
       }
@@ -293,6 +299,10 @@ __global__ void __launch_bounds__(32 * P) delta_rule_kernel(const float* __restr
 #pragma unroll
       for (int r = 0; r < SLICE / 4; ++r) {
         const float4 kv = kheld[r] = ks[r], qv = qs[r];
+        if (CH) {                             // the rows' own decays first: what follows reads the decayed state
+          const float4 gv = ((const float4*)(kq[buf][j][CH ? 2 : 0] + part * (SLICE + 4)))[r];
+          S[4 * r] *= gv.x; S[4 * r + 1] *= gv.y; S[4 * r + 2] *= gv.z; S[4 * r + 3] *= gv.w;
+        }
         sk = fmaf(S[4 * r], kv.x, sk); sk2 = fmaf(S[4 * r + 1], kv.y, sk2); sk = fmaf(S[4 * r + 2], kv.z, sk); sk2 = fmaf(S[4 * r + 3], kv.w, sk2);
         sq = fmaf(S[4 * r], qv.x, sq); sq2 = fmaf(S[4 * r + 1], qv.y, sq2); sq = fmaf(S[4 * r + 2], qv.z, sq); sq2 = fmaf(S[4 * r + 3], qv.w, sq2);
       }
@@ -355,8 +365,30 @@ GB_EXPORT int gb_delta_rule(const float* q, const float* k, const float* v, long
   if (G <= 0 || H % G || V <= 0 || D <= 0 || D > 8 * SLICE || ((uintptr_t)state & 15)) return GB_ERR_SIZE;
   dim3 grid(nseq, H, (V + 31) / 32);
 #define GB_DELTA(P)                                                                                                    \
-  launch_scan(delta_rule_kernel<P>, grid, 32 * P, stream, q, k, v, ld, beta_logit, a_logit, ldg, A_log, dt_bias, state, cu, \
+  launch_scan(delta_rule_kernel<P, false>, grid, 32 * P, stream, q, k, v, ld, beta_logit, a_logit, ldg, ldg, A_log, dt_bias, state, cu, \
               seq_slot, y, H, G, D, V, qscale)
+  switch (lanes_for(D)) {
+    case 1: GB_DELTA(1); break;
+    case 2: GB_DELTA(2); break;
+    case 4: GB_DELTA(4); break;
+    default: GB_DELTA(8);
+  }
+#undef GB_DELTA
+  return gb_launch_status();
+}
+
+// The delta rule with a decay per head and key channel: decay [ntok, H * D] rows of ldd floats, the
+// numbers g in (0, 1] themselves; beta_logit rows of ldb floats.  The rest as gb_delta_rule.
+GB_EXPORT int gb_channel_delta_rule(const float* q, const float* k, const float* v, long long ld, const float* beta_logit,
+                                    long long ldb, const float* decay, long long ldd, float* state, const int* cu,
+                                    const int* seq_slot, float* y, int nseq, int H, int G, int D, int V, float qscale,
+                                    cudaStream_t stream) {
+  if (nseq <= 0) return 0;
+  if (G <= 0 || H % G || V <= 0 || D <= 0 || D > 8 * SLICE || ((uintptr_t)state & 15) || !decay) return GB_ERR_SIZE;
+  dim3 grid(nseq, H, (V + 31) / 32);
+#define GB_DELTA(P)                                                                                                    \
+  launch_scan(delta_rule_kernel<P, true>, grid, 32 * P, stream, q, k, v, ld, beta_logit, decay, ldb, ldd, (const float*)nullptr, \
+              (const float*)nullptr, state, cu, seq_slot, y, H, G, D, V, qscale)
   switch (lanes_for(D)) {
     case 1: GB_DELTA(1); break;
     case 2: GB_DELTA(2); break;
@@ -476,13 +508,15 @@ GB_EXPORT int gb_ssd_scan(const float* x, const float* Bm, const float* Cm, long
 
 // ------------------------------------------------------------------ gated RMS norm over groups of channels
 // Row t of y [T, n] is cut into groups of gs channels, each divided by its own root mean square;
-// channel i is weighed by w[i % wn] and gated by silu(gate[t, i]).  gate_first: the gate is
-// multiplied in before the statistics are taken (the norm sees the gated values), else after.
+// channel i is weighed by w[i % wn] and gated by silu(gate[t, i]) (gate_act 0) or sigmoid(gate[t, i])
+// (gate_act 1).  gate_first: the gate is multiplied in before the statistics are taken (the norm
+// sees the gated values), else after.
+__device__ __forceinline__ float gate_f(float z, int act) { return act ? sigmoid_f(z) : silu_f(z); }
 template <typename O>
 __global__ void __launch_bounds__(128) gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ gate,
                                                               long long ldgate, const float* __restrict__ w, int wn,
                                                               O* __restrict__ out, int n, int gs, float eps, int gate_first,
-                                                              float out_scale) {
+                                                              float out_scale, int gate_act) {
   __shared__ float scratch[33];
   pdl_release_next();
   pdl_wait_prior();
@@ -491,13 +525,13 @@ __global__ void __launch_bounds__(128) gated_group_norm_kernel(const float* __re
   const float* grow = gate + (size_t)t * ldgate + base;
   float ss = 0.f;
   for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-    const float val = gate_first ? row[i] * silu_f(grow[i]) : row[i];
+    const float val = gate_first ? row[i] * gate_f(grow[i], gate_act) : row[i];
     ss = fmaf(val, val, ss);
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)gs + eps);
   for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-    const float gt = silu_f(grow[i]);
+    const float gt = gate_f(grow[i], gate_act);
     const float val = gate_first ? row[i] * gt * inv * w[(base + i) % wn] : row[i] * inv * w[(base + i) % wn] * gt;
     out[(size_t)t * n + base + i] = from_f32<O>(val * out_scale);
   }
@@ -509,7 +543,7 @@ template <typename O>
 __global__ void __launch_bounds__(256) gated_group_norm_warp_kernel(const float* __restrict__ y, const float* __restrict__ gate,
                                                                    long long ldgate, const float* __restrict__ w, int wn,
                                                                    O* __restrict__ out, int n, int gs, float eps, int gate_first,
-                                                                   float out_scale) {
+                                                                   float out_scale, int gate_act) {
   pdl_release_next();
   pdl_wait_prior();
   const int t = blockIdx.x, group = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -522,7 +556,7 @@ __global__ void __launch_bounds__(256) gated_group_norm_warp_kernel(const float*
   for (int e = 0; e < 2; ++e) {
     const int i = lane + 32 * e;
     val[e] = i < gs ? row[i] : 0.f;
-    gt[e] = i < gs ? silu_f(grow[i]) : 0.f;
+    gt[e] = i < gs ? gate_f(grow[i], gate_act) : 0.f;
     if (gate_first) val[e] *= gt[e];
     ss = fmaf(val[e], val[e], ss);
   }
@@ -537,9 +571,9 @@ __global__ void __launch_bounds__(256) gated_group_norm_warp_kernel(const float*
   }
 }
 
-GB_EXPORT int gb_gated_group_norm(const float* y, const float* gate, long long ldgate, const float* w, int wn, void* out,
-                                  int out_dtype, int ntok, int n, int gs, float eps, int gate_first, float out_scale,
-                                  cudaStream_t stream) {
+GB_EXPORT int gb_gated_group_norm_act(const float* y, const float* gate, long long ldgate, const float* w, int wn, void* out,
+                                      int out_dtype, int ntok, int n, int gs, float eps, int gate_first, float out_scale,
+                                      int gate_act, cudaStream_t stream) {
   if (ntok <= 0) return 0;
   if (gs <= 0 || n % gs || wn <= 0) return GB_ERR_SIZE;
   if (out_dtype != GB_F32 && out_dtype != GB_BF16) return GB_ERR_DTYPE;
@@ -547,23 +581,29 @@ GB_EXPORT int gb_gated_group_norm(const float* y, const float* gate, long long l
     dim3 wgrid(ntok, (n / gs + 7) / 8);
     if (out_dtype == GB_F32)
       gb_launch(gated_group_norm_warp_kernel<float>, wgrid, 256, 0, stream, y, gate, ldgate, w, wn, (float*)out, n, gs, eps,
-                gate_first, out_scale);
+                gate_first, out_scale, gate_act);
     else
       gb_launch(gated_group_norm_warp_kernel<bf16>, wgrid, 256, 0, stream, y, gate, ldgate, w, wn, (bf16*)out, n, gs, eps,
-                gate_first, out_scale);
+                gate_first, out_scale, gate_act);
     return gb_launch_status();
   }
   dim3 grid(ntok, n / gs);
   const int threads = gs <= 32 ? 32 : (gs <= 64 ? 64 : 128);
   if (out_dtype == GB_F32)
     gb_launch(gated_group_norm_kernel<float>, grid, threads, 0, stream, y, gate, ldgate, w, wn, (float*)out, n, gs, eps,
-              gate_first, out_scale);
+              gate_first, out_scale, gate_act);
   else if (out_dtype == GB_BF16)
     gb_launch(gated_group_norm_kernel<bf16>, grid, threads, 0, stream, y, gate, ldgate, w, wn, (bf16*)out, n, gs, eps, gate_first,
-              out_scale);
+              out_scale, gate_act);
   else
     return GB_ERR_DTYPE;
   return gb_launch_status();
+}
+
+GB_EXPORT int gb_gated_group_norm(const float* y, const float* gate, long long ldgate, const float* w, int wn, void* out,
+                                  int out_dtype, int ntok, int n, int gs, float eps, int gate_first, float out_scale,
+                                  cudaStream_t stream) {
+  return gb_gated_group_norm_act(y, gate, ldgate, w, wn, out, out_dtype, ntok, n, gs, eps, gate_first, out_scale, 0, stream);
 }
 
 // ------------------------------------------------------------------ mixes with the token before
@@ -645,9 +685,17 @@ __device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
     v[2 * e + 1] = __uint_as_float(u[e] & 0xffff0000u);
   }
 }
+// Other forms of the same two-step projection (``mode``), z going in as it is (no tanh):
+//   LR_RATE:     exp(-exp(rate[c / rate_group]) * softplus(a + base[c]))   a step size per channel, a rate per group
+//   LR_SIGMOID_ROOT: sigmoid(a + base[c])^(1 / tau) = exp(-softplus(-(a + base[c])) / tau)
+//   LR_PLAIN:    a + base[c]
+// with a = sum_j W[c, j] z[t, j]; base may be null (zeros).
+enum { LR_TANH_EXPEXP = 0, LR_RATE = 1, LR_SIGMOID_ROOT = 2, LR_PLAIN = 3 };
 template <typename T>
-__global__ void __launch_bounds__(128) lowrank_decay_kernel(const float* __restrict__ z, int rank, const T* __restrict__ W,
-                                                           const float* __restrict__ base, float* __restrict__ w, int ntok, int C) {
+__global__ void __launch_bounds__(128) lowrank_decay_kernel(const float* __restrict__ z, long long ldz, int rank,
+                                                           const T* __restrict__ W, const float* __restrict__ base,
+                                                           float* __restrict__ w, int ntok, int C, int mode,
+                                                           const float* __restrict__ rate, int rate_group, float inv_tau) {
   __shared__ __align__(16) float th[DEC_TOK][DEC_RC];      // tanh(z[t0 + tt, j0 + j]), zeros beyond the edges
   pdl_release_next();
   pdl_wait_prior();
@@ -663,7 +711,8 @@ __global__ void __launch_bounds__(128) lowrank_decay_kernel(const float* __restr
     __syncthreads();
     for (int i = threadIdx.x; i < DEC_TOK * DEC_RC; i += 128) {
       const int tt = i / DEC_RC, j = i % DEC_RC;
-      th[tt][j] = (tt < n && j < nj) ? tanhf(z[(size_t)(t0 + tt) * rank + j0 + j]) : 0.f;
+      const float zin = (tt < n && j < nj) ? z[(size_t)(t0 + tt) * ldz + j0 + j] : 0.f;
+      th[tt][j] = mode == LR_TANH_EXPEXP ? tanhf(zin) : zin;
     }
     __syncthreads();
     for (int j = 0; j < nj; j += 8) {
@@ -689,26 +738,48 @@ __global__ void __launch_bounds__(128) lowrank_decay_kernel(const float* __restr
     }
   }
   if (c >= C) return;
-  const float b = base[c];
+  const float b = base ? base[c] : 0.f;
+  const float rt = mode == LR_RATE ? expf(rate[c / rate_group]) : 0.f;
 #pragma unroll
   for (int tt = 0; tt < DEC_TOK; ++tt)
-    if (tt < n) w[(size_t)(t0 + tt) * C + c] = expf(-expf(acc[tt] + b));
+    if (tt < n) {
+      const float a = acc[tt] + b;
+      float r;
+      if (mode == LR_TANH_EXPEXP) r = expf(-expf(a));
+      else if (mode == LR_RATE) r = expf(-rt * softplus_f(a));
+      else if (mode == LR_SIGMOID_ROOT) r = expf(-softplus_f(-a) * inv_tau);
+      else r = a;
+      w[(size_t)(t0 + tt) * C + c] = r;
+    }
 }
 
 // z: [ntok, rank] float32; W: [C, rank] float32 or bfloat16; base: [C]; w: [ntok, C] float32.
-GB_EXPORT int gb_lowrank_decay(const float* z, int rank, const void* W, int w_dtype, const float* base, float* w, int ntok,
-                               int C, cudaStream_t stream) {
+// The general form (see the modes above): z rows of ldz floats; rate [C / rate_group] for LR_RATE;
+// tau for LR_SIGMOID_ROOT.
+GB_EXPORT int gb_lowrank_map(const float* z, long long ldz, int rank, const void* W, int w_dtype, const float* base, float* w,
+                             int ntok, int C, int mode, const float* rate, int rate_group, float tau, cudaStream_t stream) {
   if (ntok <= 0) return 0;
-  if (rank <= 0 || rank > 8192 || C <= 0) return GB_ERR_SIZE;
+  if (rank <= 0 || rank > 8192 || C <= 0 || mode < LR_TANH_EXPEXP || mode > LR_PLAIN) return GB_ERR_SIZE;
+  if (mode == LR_RATE && (!rate || rate_group <= 0)) return GB_ERR_ARG;
+  if (mode == LR_SIGMOID_ROOT && !(tau > 0.f)) return GB_ERR_ARG;
+  if (mode == LR_TANH_EXPEXP && !base) return GB_ERR_ARG;
   const dim3 grid((C + 127) / 128, (ntok + DEC_TOK - 1) / DEC_TOK);
   if (grid.y > 65535) return GB_ERR_SIZE;
+  const float inv_tau = mode == LR_SIGMOID_ROOT ? 1.0f / tau : 0.f;
   if (w_dtype == GB_F32)
-    gb_launch(lowrank_decay_kernel<float>, grid, 128, 0, stream, z, rank, (const float*)W, base, w, ntok, C);
+    gb_launch(lowrank_decay_kernel<float>, grid, 128, 0, stream, z, ldz, rank, (const float*)W, base, w, ntok, C, mode, rate,
+              rate_group, inv_tau);
   else if (w_dtype == GB_BF16)
-    gb_launch(lowrank_decay_kernel<bf16>, grid, 128, 0, stream, z, rank, (const bf16*)W, base, w, ntok, C);
+    gb_launch(lowrank_decay_kernel<bf16>, grid, 128, 0, stream, z, ldz, rank, (const bf16*)W, base, w, ntok, C, mode, rate,
+              rate_group, inv_tau);
   else
     return GB_ERR_DTYPE;
   return gb_launch_status();
+}
+
+GB_EXPORT int gb_lowrank_decay(const float* z, int rank, const void* W, int w_dtype, const float* base, float* w, int ntok,
+                               int C, cudaStream_t stream) {
+  return gb_lowrank_map(z, rank, rank, W, w_dtype, base, w, ntok, C, LR_TANH_EXPEXP, nullptr, 1, 0.f, stream);
 }
 
 // ------------------------------------------------------------------ linear attention with a decay per key channel
@@ -719,12 +790,14 @@ GB_EXPORT int gb_lowrank_decay(const float* z, int rank, const void* W, int w_dt
 // The read-out sees the state as the tokens before left it.  Tokens come in groups of GR by
 // asynchronous copies, a group ahead; the sum over r u k is taken for the group at once, a token
 // a warp.  Everything is float32.
-template <int P, int GR>
+// AFTER (no bonus): the read-out follows the write, S <- diag(w) S + k v^T; y = S^T r, which is the
+// recurrence of gated linear attention.
+template <int P, int GR, bool AFTER>
 __global__ void __launch_bounds__(32 * P) wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
-                                                         const float* __restrict__ w, long long ld, const float* __restrict__ v,
-                                                         long long ldv, const float* __restrict__ bonus, float* __restrict__ state,
+                                                         const float* __restrict__ w, long long ld, long long ldw,
+                                                         const float* __restrict__ v, long long ldv, const float* __restrict__ bonus, float* __restrict__ state,
                                                          const int* __restrict__ cu, const int* __restrict__ seq_slot,
-                                                         float* __restrict__ y, int H, int D, int V) {
+                                                         float* __restrict__ y, int H, int D, int V, float yscale) {
   constexpr int DP = P * SLICE;
   __shared__ __align__(16) float rkw[2][GR][3][padded_size(P)];   // [buffer][token][r | k | w][dims, padded]
   __shared__ float vs[2][GR][32];
@@ -742,7 +815,7 @@ __global__ void __launch_bounds__(32 * P) wkv_scan_kernel(const float* __restric
     const float4 s4 = live ? Sg[((size_t)q * V + col) * P + part] : make_float4(0.f, 0.f, 0.f, 0.f);
     S[4 * q] = s4.x; S[4 * q + 1] = s4.y; S[4 * q + 2] = s4.z; S[4 * q + 3] = s4.w;
   }
-  us[padded(tid)] = tid < D ? bonus[(size_t)head * D + tid] : 0.f;
+  us[padded(tid)] = (!AFTER && tid < D) ? bonus[(size_t)head * D + tid] : 0.f;
   if (tid >= D)      // the dims beyond the head's are zeros, written once
     for (int j = 0; j < 2 * GR; ++j)
       rkw[j / GR][j % GR][0][padded(tid)] = rkw[j / GR][j % GR][1][padded(tid)] = rkw[j / GR][j % GR][2][padded(tid)] = 0.f;
@@ -752,7 +825,7 @@ __global__ void __launch_bounds__(32 * P) wkv_scan_kernel(const float* __restric
       if (tid < D) {
         copy_async4(&rkw[buf][j][0][padded(tid)], r + t * ld + head * D + tid);
         copy_async4(&rkw[buf][j][1][padded(tid)], k + t * ld + head * D + tid);
-        copy_async4(&rkw[buf][j][2][padded(tid)], w + t * ld + head * D + tid);
+        copy_async4(&rkw[buf][j][2][padded(tid)], w + t * ldw + head * D + tid);
       }
       if (live && part == 0) copy_async4(&vs[buf][j][tid / P], v + t * ldv + head * V + col);
     }
@@ -769,13 +842,15 @@ __global__ void __launch_bounds__(32 * P) wkv_scan_kernel(const float* __restric
     }
     __syncthreads();
     const int n = min(GR, t1 - first);
-    for (int j = warp; j < n; j += P) {       // a token a warp: what the state has no part in
-      float s = 0.f;
-      for (int i = lane; i < DP; i += 32) s = fmaf(rkw[buf][j][0][padded(i)] * us[padded(i)], rkw[buf][j][1][padded(i)], s);
-      s = warp_sum(s);
-      if (lane == 0) ruk[j] = s;
+    if (!AFTER) {
+      for (int j = warp; j < n; j += P) {       // a token a warp: what the state has no part in
+        float s = 0.f;
+        for (int i = lane; i < DP; i += 32) s = fmaf(rkw[buf][j][0][padded(i)] * us[padded(i)], rkw[buf][j][1][padded(i)], s);
+        s = warp_sum(s);
+        if (lane == 0) ruk[j] = s;
+      }
+      __syncthreads();
     }
-    __syncthreads();
     for (int j = 0; j < n; ++j) {
       const float4* rs = (const float4*)(rkw[buf][j][0] + part * (SLICE + 4));
       const float4* ks = (const float4*)(rkw[buf][j][1] + part * (SLICE + 4));
@@ -785,15 +860,21 @@ __global__ void __launch_bounds__(32 * P) wkv_scan_kernel(const float* __restric
 #pragma unroll
       for (int q = 0; q < SLICE / 4; ++q) {
         const float4 rv = rs[q], kv = ks[q], wv = ws[q];
-        sr = fmaf(S[4 * q], rv.x, sr); sr2 = fmaf(S[4 * q + 1], rv.y, sr2);
-        sr = fmaf(S[4 * q + 2], rv.z, sr); sr2 = fmaf(S[4 * q + 3], rv.w, sr2);
+        if (!AFTER) {
+          sr = fmaf(S[4 * q], rv.x, sr); sr2 = fmaf(S[4 * q + 1], rv.y, sr2);
+          sr = fmaf(S[4 * q + 2], rv.z, sr); sr2 = fmaf(S[4 * q + 3], rv.w, sr2);
+        }
         S[4 * q] = fmaf(wv.x, S[4 * q], kv.x * vc);
         S[4 * q + 1] = fmaf(wv.y, S[4 * q + 1], kv.y * vc);
         S[4 * q + 2] = fmaf(wv.z, S[4 * q + 2], kv.z * vc);
         S[4 * q + 3] = fmaf(wv.w, S[4 * q + 3], kv.w * vc);
+        if (AFTER) {
+          sr = fmaf(S[4 * q], rv.x, sr); sr2 = fmaf(S[4 * q + 1], rv.y, sr2);
+          sr = fmaf(S[4 * q + 2], rv.z, sr); sr2 = fmaf(S[4 * q + 3], rv.w, sr2);
+        }
       }
       sr = lanes_sum<P>(sr + sr2);
-      if (live && part == 0) y[(size_t)(first + j) * H * V + head * V + col] = fmaf(ruk[j], vc, sr);
+      if (live && part == 0) y[(size_t)(first + j) * H * V + head * V + col] = (AFTER ? sr : fmaf(ruk[j], vc, sr)) * yscale;
     }
     __syncthreads();   // the group after next is brought into this buffer; ruk is written again
   }
@@ -805,16 +886,19 @@ __global__ void __launch_bounds__(32 * P) wkv_scan_kernel(const float* __restric
   }
 }
 
-// r, k, w: rows of ld floats, head h at h * D; v: rows of ldv floats, head h at h * V; bonus: [H, D];
+// r, k: rows of ld floats, w: rows of ldw floats, head h at h * D; v: rows of ldv floats, head h at h * V; bonus: [H, D],
+// or null for the form whose read-out follows the write;
 // state: [slots, H, gb_state_floats(D, V)] float32; y: [ntok, H * V].
-GB_EXPORT int gb_wkv_scan(const float* r, const float* k, const float* w, long long ld, const float* v, long long ldv,
-                          const float* bonus, float* state, const int* cu, const int* seq_slot, float* y, int nseq, int H, int D,
-                          int V, cudaStream_t stream) {
+// yscale multiplies every result (a factor on r, which the read-out is linear in).
+GB_EXPORT int gb_wkv_scan_scaled(const float* r, const float* k, const float* w, long long ld, long long ldw, const float* v, long long ldv,
+                                 const float* bonus, float* state, const int* cu, const int* seq_slot, float* y, int nseq, int H,
+                                 int D, int V, float yscale, cudaStream_t stream) {
   if (nseq <= 0) return 0;
   if (H <= 0 || V <= 0 || D <= 0 || D > 8 * SLICE || ((uintptr_t)state & 15)) return GB_ERR_SIZE;
   dim3 grid(nseq, H, (V + 31) / 32);
-#define GB_WKV(P, GR) \
-  launch_scan(wkv_scan_kernel<P, GR>, grid, 32 * P, stream, r, k, w, ld, v, ldv, bonus, state, cu, seq_slot, y, H, D, V)
+#define GB_WKV(P, GR)                                                                                                       \
+  if (bonus) launch_scan(wkv_scan_kernel<P, GR, false>, grid, 32 * P, stream, r, k, w, ld, ldw, v, ldv, bonus, state, cu, seq_slot, y, H, D, V, yscale); \
+  else launch_scan(wkv_scan_kernel<P, GR, true>, grid, 32 * P, stream, r, k, w, ld, ldw, v, ldv, bonus, state, cu, seq_slot, y, H, D, V, yscale)
   switch (lanes_for(D)) {
     case 1: GB_WKV(1, 8); break;
     case 2: GB_WKV(2, 8); break;
@@ -823,4 +907,10 @@ GB_EXPORT int gb_wkv_scan(const float* r, const float* k, const float* w, long l
   }
 #undef GB_WKV
   return gb_launch_status();
+}
+
+GB_EXPORT int gb_wkv_scan(const float* r, const float* k, const float* w, long long ld, const float* v, long long ldv,
+                          const float* bonus, float* state, const int* cu, const int* seq_slot, float* y, int nseq, int H, int D,
+                          int V, cudaStream_t stream) {
+  return gb_wkv_scan_scaled(r, k, w, ld, ld, v, ldv, bonus, state, cu, seq_slot, y, nseq, H, D, V, 1.0f, stream);
 }

@@ -913,7 +913,8 @@ def grouped_gemm(a, lda, a_gstride, a_rows, a_div, w, w_gstride, c, ldc, c_gstri
     """Many bfloat16 products C_g = A_g W_g^T of unequal row counts in one tensor-core launch (see
     csrc/grouped_gemm.cu): group g's rows are offsets[g]..offsets[g+1] (None: ``rows`` each), an A
     row is a_rows[i] // a_div (None: i), C is bfloat16 or float32 by its dtype; ``gated``: W_g stacks
-    gate rows over up rows and C = min(g, limit) * sigmoid(alpha g) * (clamp(u) + shift)."""
+    gate rows over up rows and C = min(g, limit) * sigmoid(alpha g) * (clamp(u) + shift); ``gated`` 2:
+    no gate rows, C = gelu(A W_g^T) in the exact (erf) form."""
     _cuda(a, w, c, scale, scale_rows, offsets, a_rows)
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and c.dtype in (torch.bfloat16, torch.float32)
     f = _fn("grouped_gemm", "gb_grouped_gemm",
@@ -922,7 +923,7 @@ def grouped_gemm(a, lda, a_gstride, a_rows, a_div, w, w_gstride, c, ldc, c_gstri
              c_float, c_float, c_void_p])
     _check(f(a.data_ptr(), lda, a_gstride, _ptr(a_rows), a_div, w.data_ptr(), w_gstride, c.data_ptr(), ldc, c_gstride,
              _ptr(scale), _ptr(scale_rows), s_rstride, s_gstride, _ptr(offsets), groups, rows, max_rows, n, k,
-             1 if gated else 0, 1 if c.dtype == torch.float32 else 0, limit, alpha, shift, _stream()), what, "matmul", nbytes)
+             int(gated), 1 if c.dtype == torch.float32 else 0, limit, alpha, shift, _stream()), what, "matmul", nbytes)
 
 
 def latent_attention_ref(qa, out, heads, rank, rd, cache, page_table, page_size, tok_pos, tok_seq, seq_slot, window=None,
@@ -1054,10 +1055,11 @@ def latent_attention_units(compute: str, rank: int, rd: int, dim: int = 0, vd: i
 
 # --------------------------------------------------------------------------- routed feed-forward
 
-def moe_topk(z, bias, experts, top, has_gate=False):
+def moe_topk(z, bias, experts, top, has_gate=False, all_softmax=False):
     """(idx int32 [T, top], weights float32 [T, top], shared float32 [T] or None) from the router's
     logits z (float32 [T, experts (+ 1)]): each token's ``top`` largest z + bias (the lower index wins
-    a tie), the softmax over those alone, and with ``has_gate`` the sigmoid of column ``experts``."""
+    a tie), the softmax over those alone (with ``all_softmax``: their shares of the softmax over all
+    experts, which do not add up to one), and with ``has_gate`` the sigmoid of column ``experts``."""
     _cuda(z, bias)
     t = z.shape[0]
     assert z.dtype == torch.float32 and z.stride(1) == 1 and z.shape[1] >= experts + (1 if has_gate else 0)
@@ -1065,10 +1067,10 @@ def moe_topk(z, bias, experts, top, has_gate=False):
     idx = torch.empty((t, top), dtype=torch.int32, device=z.device)
     wts = torch.empty((t, top), dtype=torch.float32, device=z.device)
     sg = torch.empty((t,), dtype=torch.float32, device=z.device) if has_gate else None
-    f = _fn("moe", "gb_moe_topk", [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                   c_void_p])
+    f = _fn("moe", "gb_moe_topk_mode", [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                        c_int, c_int, c_void_p])
     _check(f(z.data_ptr(), z.stride(0), _ptr(bias), idx.data_ptr(), wts.data_ptr(), _ptr(sg), t, experts, top,
-             1 if has_gate else 0, _stream()), "moe_topk", "elementwise", _nbytes(z))
+             1 if has_gate else 0, 1 if all_softmax else 0, _stream()), "moe_topk", "elementwise", _nbytes(z))
     return idx, wts, sg
 
 
@@ -1102,6 +1104,84 @@ def moe_experts(h, idx, wts, sg, w_gate_up, w_down, shared_gate_up, shared_down,
              _ptr(shared_down), rows.data_ptr(), residual.data_ptr(), residual.stride(0), t, width, ff, ffs, top, _stream()),
            "moe_down", "matmul", _nbytes(y) + 2 * _nbytes(rows) + 2 * t * width * 4 + t * slots * ff * width * h.element_size())
     count_launches(1)   # the kernel that adds a token's rows
+
+
+def moe_experts_plain(h, idx, wts, w_up, w_down, residual):
+    """residual[t] += sum_k wts[t, k] * down_{idx[t, k]} gelu(up_{idx[t, k]} h[t]) for experts without a
+    gate (exact GELU), token-major.  w_up [E, ff, width], w_down [E, width, ff]."""
+    _cuda(h, idx, wts, w_up, w_down, residual)
+    t, width = h.shape
+    e, ff, _ = w_up.shape
+    top = idx.shape[1]
+    assert w_up.is_contiguous() and w_down.is_contiguous() and w_down.shape == (e, width, ff) and w_up.shape[2] == width
+    assert w_up.dtype == h.dtype == w_down.dtype and residual.dtype == torch.float32 and residual.stride(1) == 1
+    y = torch.empty((t, top, ff), dtype=h.dtype, device=h.device)
+    f = _fn("moe", "gb_moe_up", [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(h.data_ptr(), h.stride(0), dtype_code(h.dtype), idx.data_ptr(), w_up.data_ptr(), y.data_ptr(), t, width, ff, top,
+             _stream()), "moe_up", "matmul", _nbytes(h, y) + t * top * ff * width * h.element_size())
+    rows = torch.empty((t, top, width), dtype=torch.float32, device=h.device)
+    f = _fn("moe", "gb_moe_down", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(y.data_ptr(), dtype_code(h.dtype), idx.data_ptr(), wts.data_ptr(), None, w_down.data_ptr(), None,
+             rows.data_ptr(), residual.data_ptr(), residual.stride(0), t, width, ff, 0, top, _stream()),
+           "moe_down", "matmul", _nbytes(y) + 2 * _nbytes(rows) + 2 * t * width * 4 + t * top * ff * width * h.element_size())
+    count_launches(1)   # the kernel that adds a token's rows
+
+
+def moe_experts_plain_grouped(h, idx, wts, w_up, w_down, residual):
+    """As moe_experts_plain for a step of many tokens: entries ordered by expert, two grouped
+    tensor-core products (up with the GELU in its epilogue, down scaled by the routing weights), a
+    token's rows added into the residual in slot order."""
+    _cuda(h, idx, wts, w_up, w_down, residual)
+    t, width = h.shape
+    e, ff, _ = w_up.shape
+    top = idx.shape[1]
+    entries = t * top
+    assert residual.dtype == torch.float32 and residual.stride(1) == 1 and idx.is_contiguous() and wts.is_contiguous()
+    meta = torch.empty(e + 1 + 2 * entries, dtype=torch.int32, device=h.device)
+    offsets, perm, place = meta[:e + 1], meta[e + 1:e + 1 + entries], meta[e + 1 + entries:]
+    f = _fn("grouped_gemm", "gb_moe_sort", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(idx.data_ptr(), entries, e, offsets.data_ptr(), perm.data_ptr(), place.data_ptr(), _stream()), "moe_sort",
+           "elementwise", 3 * entries * 4)
+    y = torch.empty((entries, ff), dtype=torch.bfloat16, device=h.device)
+    grouped_gemm(h, h.stride(0), 0, perm, top, w_up, ff * width, y, ff, 0, None, None, 0, 0, offsets, e, 0, entries,
+                 ff, width, gated=2, what="moe_up_tc", nbytes=_nbytes(w_up, y) + entries * width * 2)
+    rows = torch.empty((entries, width), dtype=torch.float32, device=h.device)
+    grouped_gemm(y, ff, 0, None, 1, w_down, width * ff, rows, width, 0, wts.view(-1), perm, 1, 0, offsets, e, 0, entries,
+                 width, ff, what="moe_down_tc", nbytes=_nbytes(w_down, y, rows))
+    f = _fn("grouped_gemm", "gb_moe_combine", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
+    _check(f(rows.data_ptr(), place.data_ptr(), residual.data_ptr(), residual.stride(0), t, width, top, _stream()),
+           "moe_combine", "elementwise", _nbytes(rows) + 2 * t * width * 4)
+
+
+def moe_experts_plain_tc(h, idx, wts, w_up, w_down, residual):
+    """As moe_experts_plain_grouped for a prompt step, the two products on the tcgen05 kernel (the
+    activations copied into an order in which every expert's rows start at a multiple of the
+    tile's tokens; the GELU and the routing weight in the first product's epilogue)."""
+    _cuda(h, idx, wts, w_up, w_down, residual)
+    t, width = h.shape
+    e, ff, _ = w_up.shape
+    top, bn = idx.shape[1], MOE_TC_TILE
+    entries = t * top
+    rows = (-(-entries // bn) + e) * bn
+    meta = torch.empty(rows // bn + entries + rows, dtype=torch.int32, device=h.device)
+    tile_expert, place, row_entry = meta[:rows // bn], meta[rows // bn:rows // bn + entries], meta[rows // bn + entries:]
+    f = _fn("grouped_gemm", "gb_moe_sort_padded", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(idx.data_ptr(), entries, e, bn, rows, tile_expert.data_ptr(), place.data_ptr(), row_entry.data_ptr(), _stream()),
+           "moe_sort", "elementwise", 3 * entries * 4)
+    xp = torch.empty((rows, width), dtype=torch.bfloat16, device=h.device)
+    scale = torch.empty((rows,), dtype=torch.float32, device=h.device)
+    f = _fn("grouped_gemm", "gb_moe_permute", [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                               c_int, c_int, c_int, c_void_p])
+    _check(f(h.data_ptr(), h.stride(0), row_entry.data_ptr(), tile_expert.data_ptr(), wts.data_ptr(), xp.data_ptr(),
+             scale.data_ptr(), rows, width, top, bn, _stream()), "moe_permute", "elementwise", 2 * entries * width * 2)
+    y = torch.empty((rows, ff), dtype=torch.bfloat16, device=h.device)
+    gemm_tc_grouped(xp, w_up.view(e * ff, width), y, ff, e, tile_expert, scale, gelu=True)
+    out = torch.empty((rows, width), dtype=torch.float32, device=h.device)
+    gemm_tc_grouped(y, w_down.view(e * width, ff), out, width, e, tile_expert)
+    f = _fn("grouped_gemm", "gb_moe_combine", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
+    _check(f(out.data_ptr(), place.data_ptr(), residual.data_ptr(), residual.stride(0), t, width, top, _stream()),
+           "moe_combine", "elementwise", entries * width * 4 + 2 * t * width * 4)
 
 
 MOE_GROUPED_MIN_TOKENS = 16
@@ -1156,20 +1236,22 @@ def moe_tc_usable(h, w_gate_up, w_down) -> bool:
 
 
 def gemm_tc_grouped(x, w, y, n, experts, tile_expert, row_scale=None, gated=False, limit=0.0, alpha=0.0, shift=0.0,
-                    bn=MOE_TC_TILE):
+                    bn=MOE_TC_TILE, gelu=False):
     """The tcgen05 product over groups of rows: x [rows, K] holds the groups one after the other, each
     starting at a multiple of ``bn`` rows; w stacks the groups' matrices ([experts * n, K], or
     [experts * 2 n, K] gated); tile_expert names the group of every tile of ``bn`` rows (-1: none).
-    y float32 [rows, n], or with ``gated`` bfloat16 [rows, n] = row_scale * act(gate, up)."""
+    y float32 [rows, n], or with ``gated`` bfloat16 [rows, n] = row_scale * act(gate, up), or with
+    ``gelu`` bfloat16 [rows, n] = row_scale * gelu(x w^T) (erf form, no gate rows)."""
     _cuda(x, w, y, tile_expert, row_scale)
     rows, k = x.shape
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous()
-    assert y.shape == (rows, n) and y.is_contiguous() and y.dtype == (torch.bfloat16 if gated else torch.float32)
+    assert not (gated and gelu)
+    assert y.shape == (rows, n) and y.is_contiguous() and y.dtype == (torch.bfloat16 if gated or gelu else torch.float32)
     assert tile_expert.dtype == torch.int32 and tile_expert.numel() == rows // bn and rows % bn == 0
     f = _fn("gemm_tc", "gb_gemm_tc_grouped",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p,
              c_void_p, c_float, c_float, c_float, c_void_p])
-    _check(f(x.data_ptr(), w.data_ptr(), y.data_ptr(), 3 if gated else 1, rows, n, k, x.stride(0), y.stride(0), bn,
+    _check(f(x.data_ptr(), w.data_ptr(), y.data_ptr(), 3 if gated else (0 if gelu else 1), rows, n, k, x.stride(0), y.stride(0), bn,
              sm_count(x.device), experts, tile_expert.data_ptr(), _ptr(row_scale), limit, alpha, shift, _stream()),
            "gemm_tc_grouped", "matmul", _nbytes(x, w, y))
 
@@ -1514,19 +1596,25 @@ def ssd_scan(x, b, c, dt_raw, a_log, dt_bias, skip, state, cu_seqlens, seq_slot,
              _stream()), "ssd_scan", "attention", _nbytes(y) * 2 + 2 * seq_slot.numel() * heads * n_state * vdim * 4)
 
 
-def gated_group_norm(y, gate, weight, out, group_size: int, eps: float, gate_first: bool, out_scale: float = 1.0):
+GATE_ACTS = {"silu": 0, "sigmoid": 1}
+
+
+def gated_group_norm(y, gate, weight, out, group_size: int, eps: float, gate_first: bool, out_scale: float = 1.0,
+                     gate_act: str = "silu"):
     """Rows of float32 ``y`` [T, n] in groups of ``group_size`` channels, each group divided by its
-    root mean square, channel i times weight[i % len(weight)] and silu(gate[t, i]); with
-    ``gate_first`` the gate goes in before the statistics.  ``gate``: float32, may be a slice."""
+    root mean square, channel i times weight[i % len(weight)] and silu(gate[t, i]) (or, with
+    ``gate_act`` "sigmoid", sigmoid(gate[t, i])); with ``gate_first`` the gate goes in before the
+    statistics.  ``gate``: float32, may be a slice."""
     _cuda(y, gate, weight, out)
     assert y.dtype == torch.float32 and gate.dtype == torch.float32 and weight.dtype == torch.float32
     assert y.is_contiguous() and out.is_contiguous() and out.shape == y.shape and gate.shape == y.shape
     gp, ldg = _cols(gate)
-    f = _fn("recurrent", "gb_gated_group_norm",
+    f = _fn("recurrent", "gb_gated_group_norm_act",
             [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_float,
-             c_void_p])
+             c_int, c_void_p])
     _check(f(y.data_ptr(), gp, ldg, weight.data_ptr(), weight.numel(), out.data_ptr(), dtype_code(out.dtype), y.shape[0],
-             y.shape[1], group_size, eps, 1 if gate_first else 0, out_scale, _stream()), "gated_group_norm", "norm",
+             y.shape[1], group_size, eps, 1 if gate_first else 0, out_scale, GATE_ACTS[gate_act], _stream()),
+           "gated_group_norm", "norm",
            _nbytes(y, out) + y.numel() * 4)
 
 
@@ -1565,37 +1653,97 @@ def lowrank_decay(z, w2, base):
     return out
 
 
-def wkv_scan(r, k, w, v, bonus, state, cu_seqlens, seq_slot, y, heads, dim, vdim):
+LOWRANK_MODES = {"tanh_expexp": 0, "rate": 1, "sigmoid_root": 2, "plain": 3}
+
+
+def lowrank_map(z, w2, base, mode: str, rate=None, rate_group: int = 1, tau: float = 1.0):
+    """float32 [T, C] from the second half of a two-matrix projection, a = z @ w2.T + base in float32
+    (``z`` float32 [T, rank], may be a slice of columns; ``base`` float32 [C] or None), by ``mode``:
+    "rate": exp(-exp(rate[c // rate_group]) * softplus(a)); "sigmoid_root": sigmoid(a) ** (1 / tau);
+    "plain": a; "tanh_expexp": exp(-exp(tanh(z) @ w2.T + base)) (lowrank_decay)."""
+    _cuda(z, w2, base, rate)
+    c, rank = w2.shape
+    assert z.dtype == torch.float32 and z.shape[1] == rank and w2.is_contiguous()
+    assert base is None or (base.dtype == torch.float32 and base.numel() == c)
+    assert rate is None or (rate.dtype == torch.float32 and rate.is_contiguous() and rate.numel() * rate_group == c)
+    zp, ldz = _cols(z)
+    out = torch.empty((z.shape[0], c), dtype=torch.float32, device=z.device)
+    f = _fn("recurrent", "gb_lowrank_map", [c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                            c_int, c_void_p, c_int, c_float, c_void_p])
+    _check(f(zp, ldz, rank, w2.data_ptr(), dtype_code(w2.dtype), _ptr(base), out.data_ptr(), z.shape[0], c,
+             LOWRANK_MODES[mode], _ptr(rate), rate_group, float(tau), _stream()), "lowrank_map", "elementwise",
+           _nbytes(out, w2) + z.shape[0] * rank * 4)
+    return out
+
+
+def channel_delta_rule(q, k, v, beta_logit, decay, state, cu_seqlens, seq_slot, y, heads, groups, dim, vdim, q_scale):
+    """The delta rule with a decay per head and key channel over each sequence of the packed step
+    (float32 throughout): S <- diag(g) S; u = beta (v - S^T k^); S <- S + k^ u^T; y = S^T q^, with k^,
+    q^ the unit vectors of k and q (q^ times ``q_scale``), beta = sigmoid(beta_logit), g = ``decay``
+    [T, heads * dim] as given.  q, k, v: slices of columns of one [T, *] tensor, q/k head
+    i // (heads / groups) for head i; ``state`` as for delta_rule; dim up to 256."""
+    _cuda(q, k, v, beta_logit, decay, state, cu_seqlens, seq_slot, y)
+    for t in (q, k, v, beta_logit, decay, y, state):
+        assert t.dtype == torch.float32
+    qp, ld = _cols(q)
+    kp, ldk = _cols(k)
+    vp, ldv = _cols(v)
+    bp, ldb = _cols(beta_logit)
+    dp, ldd = _cols(decay)
+    assert ld == ldk == ldv and y.is_contiguous() and y.shape[1] == heads * vdim and decay.shape[1] == heads * dim
+    assert state.is_contiguous() and tuple(state.shape[1:]) == (heads, recurrent_state_floats(dim, vdim))
+    f = _fn("recurrent", "gb_channel_delta_rule",
+            [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(qp, kp, vp, ld, bp, ldb, dp, ldd, state.data_ptr(), cu_seqlens.data_ptr(), seq_slot.data_ptr(), y.data_ptr(),
+             seq_slot.numel(), heads, groups, dim, vdim, q_scale, _stream()),
+           "channel_delta_rule", "attention", _nbytes(y) * 2 + _nbytes(decay) + 2 * seq_slot.numel() * heads * dim * vdim * 4)
+
+
+def wkv_scan(r, k, w, v, bonus, state, cu_seqlens, seq_slot, y, heads, dim, vdim, out_scale: float = 1.0):
     """Linear attention with a decay per key channel over each sequence of the packed step (float32):
-    y = S^T r + (sum_d r_d bonus_d k_d) v, then S <- diag(w) S + k v^T, per head.  r, k, w: [T, heads *
-    dim] with equal row strides; v: [T, heads * vdim]; ``bonus`` [heads, dim]; ``state`` [slots + 1,
-    heads, recurrent_state_floats(dim, vdim)] (see recurrent_state_matrix); dim up to 256."""
+    y = S^T r + (sum_d r_d bonus_d k_d) v, then S <- diag(w) S + k v^T, per head.  r, k: [T, heads *
+    dim] with equal row strides; w: [T, heads * dim]; v: [T, heads * vdim]; ``bonus`` [heads, dim]; ``state`` [slots + 1,
+    heads, recurrent_state_floats(dim, vdim)] (see recurrent_state_matrix); dim up to 256.
+    ``bonus`` None: the read-out follows the write, S <- diag(w) S + k v^T; y = S^T r (gated linear
+    attention).  ``out_scale`` multiplies y (a factor on r, which y is linear in)."""
     _cuda(r, k, w, v, bonus, state, cu_seqlens, seq_slot, y)
     for t in (r, k, w, v, bonus, state, y):
-        assert t.dtype == torch.float32
+        assert t is None or t.dtype == torch.float32
     rp, ld = _cols(r)
     kp, ldk = _cols(k)
     wp, ldw = _cols(w)
     vp, ldv = _cols(v)
-    assert ld == ldk == ldw and y.is_contiguous() and y.shape[1] == heads * vdim and bonus.is_contiguous()
-    assert bonus.numel() == heads * dim
+    assert ld == ldk and y.is_contiguous() and y.shape[1] == heads * vdim
+    assert bonus is None or (bonus.is_contiguous() and bonus.numel() == heads * dim)
     assert state.is_contiguous() and tuple(state.shape[1:]) == (heads, recurrent_state_floats(dim, vdim))
-    f = _fn("recurrent", "gb_wkv_scan", [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
-                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(rp, kp, wp, ld, vp, ldv, bonus.data_ptr(), state.data_ptr(), cu_seqlens.data_ptr(), seq_slot.data_ptr(),
-             y.data_ptr(), seq_slot.numel(), heads, dim, vdim, _stream()), "wkv_scan", "attention",
+    f = _fn("recurrent", "gb_wkv_scan_scaled", [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p,
+                                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                                c_void_p])
+    _check(f(rp, kp, wp, ld, ldw, vp, ldv, _ptr(bonus), state.data_ptr(), cu_seqlens.data_ptr(), seq_slot.data_ptr(),
+             y.data_ptr(), seq_slot.numel(), heads, dim, vdim, float(out_scale), _stream()), "wkv_scan", "attention",
            _nbytes(y) * 5 + 2 * seq_slot.numel() * heads * dim * vdim * 4)
 
 
 # --------------------------------------------------------------------------- attention with capped scores
 
 def filter_rope_cache(u, taps, state, inv_freq, rot, ctx_pos, tok_seq, seq_slot, cu_seqlens, page_table, page_size, q_out,
-                      kcache, vcache, heads, groups, dim, vdim):
+                      kcache, vcache, heads, groups, dim, vdim, q_norm=None, k_norm=None, norm_eps: float = 0.0,
+                      rot_magnitude: float = 1.0, q_temper=None, values_are_keys: bool = False):
     """The columns [q | k | v] of ``u`` through a short causal filter (``taps`` [channels, K] or
     None), the first ``rot`` dims of each q and k head rotated (pairs i, i + rot/2), then q into
-    ``q_out`` [T, heads * dim] and keys and values into their pages (None: not kept)."""
-    _cuda(u, taps, state, inv_freq, ctx_pos, tok_seq, seq_slot, cu_seqlens, page_table, q_out, kcache, vcache)
-    channels = (heads + groups) * dim + groups * vdim
+    ``q_out`` [T, heads * dim] and keys and values into their pages (None: not kept).
+    ``q_norm`` / ``k_norm`` (float32 [dim]): every q / k head is divided by its root mean square
+    (``norm_eps``) and multiplied by the weight before the rotation.  ``rot_magnitude`` multiplies
+    the cosines and sines.  ``q_temper`` (coef, every): q at position p times 1 + coef ln(floor((p +
+    1) / every) + 1).  ``values_are_keys``: the rows hold [q | k] alone and a value head is its key
+    head as projected and filtered, before norm and rotation (vdim == dim)."""
+    _cuda(u, taps, state, inv_freq, ctx_pos, tok_seq, seq_slot, cu_seqlens, page_table, q_out, kcache, vcache, q_norm, k_norm)
+    channels = (heads + groups) * dim + (0 if values_are_keys else groups * vdim)
+    for w in (q_norm, k_norm):
+        assert w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == dim)
+    assert not values_are_keys or vdim == dim
+    qt_coef, qt_every = (float(q_temper[0]), int(q_temper[1])) if q_temper else (0.0, 0)
     k = 0 if taps is None else taps.shape[1]
     up, ldu = _cols(u)
     qp, ldq = _cols(q_out)
@@ -1607,13 +1755,15 @@ def filter_rope_cache(u, taps, state, inv_freq, rot, ctx_pos, tok_seq, seq_slot,
     if kcache is not None:
         assert kcache.dtype == u.dtype and vcache.dtype == u.dtype and kcache.is_contiguous() and vcache.is_contiguous()
         assert tuple(kcache.shape[1:]) == (groups, page_size, dim) and tuple(vcache.shape[1:]) == (groups, vdim, page_size)
-    f = _fn("attention_capped", "gb_filter_rope_cache",
+    f = _fn("attention_capped", "gb_filter_rope_cache_ext",
             [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+             c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+             c_void_p, c_float, c_float, c_float, c_int, c_int, c_void_p])
     _check(f(up, dtype_code(u.dtype), ldu, _ptr(taps), _ptr(state) if k > 1 else None, k, _ptr(inv_freq) if rot else None,
              rot, ctx_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), cu_seqlens.data_ptr(), _ptr(page_table),
              page_table.shape[1] if page_table is not None else 1, page_size, qp, ldq, _ptr(kcache), _ptr(vcache),
-             u.shape[0], heads, groups, dim, vdim, _stream()), "filter_rope_cache", "elementwise",
+             u.shape[0], heads, groups, dim, vdim, _ptr(q_norm), _ptr(k_norm), float(norm_eps), float(rot_magnitude), qt_coef,
+             qt_every, 1 if values_are_keys else 0, _stream()), "filter_rope_cache", "elementwise",
            2 * u.numel() * u.element_size())
 
 

@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers each of them under its config.json names."""
-from . import dalerax, kuporax, qwen3, toretar  # noqa: F401
+from . import dalerax, kuporax, nogosun, qwen3, toretar  # noqa: F401

@@ -48,6 +48,9 @@ class Attention(Part):
                              "(a multiple of 16 from 16 to 256)")
         pos = p.get("position")
         self.position = build_part("position", pos, compute) if pos is not None else None
+        if getattr(self.position, "magnitude", 1.0) != 1.0:
+            raise ValueError("attention: a rotation whose cosines and sines carry a magnitude is not supported by this "
+                             "part's kernels (capped_attention takes one)")
         self.qkv = self.o = self.q_norm = self.k_norm = None
 
     # ---- weights

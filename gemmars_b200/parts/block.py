@@ -1,7 +1,7 @@
 """The arrangement of a layer's parts.
 
 ``prenorm`` (src/qwen.rs:682-696): x += mixer(norm(x)); x += ffn(norm(x)), the residual stream
-``x`` in float32.  ``parallel``: x += mixer(norm(x)) + ffn(norm(x)) with one norm.  ``sandwich``:
+``x`` in float32.  ``parallel``: x += mixer(norm(x)) + ffn(norm(x)) with one norm, or with a norm of its own for the feed-forward.  ``sandwich``:
 a norm on both sides of each sublayer, x += post(mixer(pre(x))); x += post(ffn(pre(x))).  Another
 arrangement (a third norm) is another class like these, registered under its own kind
 and reading its own part names from the layer's spec."""
@@ -56,16 +56,21 @@ class PreNormBlock(Block):
 class ParallelBlock(Block):
     """``parallel``: h = norm(x); x += mixer(h) + ffn(h).  One norm, and both branches read its
     output; each branch adds its result into the float32 residual stream, the mixer first.  The
-    layer's spec lists ``norm``, ``mixer`` and, when the layer has a feed-forward, ``ffn``."""
+    layer's spec lists ``norm``, ``mixer`` and, when the layer has a feed-forward, ``ffn``.  With
+    ``ffn_norm`` in the spec the feed-forward reads a norm of its own of the same x:
+    x += mixer(norm(x)) + ffn(ffn_norm(x)), both norms taken before either branch changes x."""
 
     def __init__(self, layer_spec, compute):
         super().__init__(layer_spec, compute)
         self.norm = self.need("norm", "norm")
         self.mixer = self.need("mixer", "mixer")
         self.ffn = self.need("ffn", "ffn") if "ffn" in layer_spec.parts else None
+        self.ffn_norm = self.need("ffn_norm", "norm") if self.ffn is not None and "ffn_norm" in layer_spec.parts else None
 
     def parts(self):
         out = {"norm": self.norm, "mixer": self.mixer}
+        if self.ffn_norm is not None:
+            out["ffn_norm"] = self.ffn_norm
         if self.ffn is not None:
             out["ffn"] = self.ffn
         return out
@@ -73,9 +78,10 @@ class ParallelBlock(Block):
     def forward(self, ctx, x, caches, writes_cache=True):
         mine = self.split_caches(caches)
         h = self.norm.forward(ctx, x)        # read by both branches before either changes x
+        h_ffn = self.ffn_norm.forward(ctx, x) if self.ffn_norm is not None else h
         self.mixer.forward(ctx, h, x, mine["mixer"], writes_cache)
         if self.ffn is not None:
-            self.ffn.forward(ctx, h, x)
+            self.ffn.forward(ctx, h_ffn, x)
 
 
 class SandwichBlock(Block):

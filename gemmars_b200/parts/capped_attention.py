@@ -20,8 +20,15 @@ False has no k and v matrices: it runs its own queries, mask and sink over the k
 the schedule entry whose cache it is given.  A window's pages are a ring only with ``ring`` (the
 default) and no kept first positions; otherwise every page stays and the window is the kernels'
 mask alone, which is what a layer needs whose cache another layer with another mask reads.
+Four more parameters, all off by default.  ``values_are_keys``: there is no W_v; a value head is
+its key head as projected (with its bias), before norm and rotation, so vdim == dim.  ``qk_norm``
+(an eps): every q and k head is divided by its root mean square and multiplied by a weight over
+its dims (``q_norm``, ``k_norm``, shared by the heads) before the rotation.  ``q_temper`` {"coef",
+"every"}: the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1).
+``fixed_sink`` (a number s): exp(s) joins the softmax's denominator for every head, without a
+tensor (0.0: one is added to the denominator).
 Parameters: hidden_size, heads, kv_heads, dim, vdim, bias, conv, window, keep_first, sink, scale,
-softcap, gate, position, has_kv, ring, out_scale.
+softcap, gate, position, has_kv, ring, out_scale, values_are_keys, qk_norm, q_temper, fixed_sink.
 """
 from __future__ import annotations
 
@@ -53,6 +60,18 @@ class CappedAttention(Part):
         self.scale = float(p["scale"]) if p.get("scale") is not None else float(self.dim) ** -0.5
         self.softcap = float(p.get("softcap") or 0.0)
         self.out_scale = float(p.get("out_scale", 1.0))
+        self.values_are_keys = bool(p.get("values_are_keys", False))
+        self.qk_norm_eps = float(p["qk_norm"]) if p.get("qk_norm") is not None else None
+        temper = p.get("q_temper")
+        self.q_temper = (float(temper["coef"]), int(temper["every"])) if temper else None
+        self.fixed_sink = float(p["fixed_sink"]) if p.get("fixed_sink") is not None else None
+        if self.values_are_keys and (self.vdim != self.dim or not self.has_kv or self.taps > 1):
+            raise ValueError("capped_attention: values that are the keys need vdim == dim, keys of the part's own and no "
+                             "filter with a memory")
+        if self.q_temper is not None and self.q_temper[1] < 1:
+            raise ValueError(f"capped_attention: q_temper.every must be at least 1, got {self.q_temper[1]}")
+        if self.sink and self.fixed_sink is not None:
+            raise ValueError("capped_attention: a learned sink and a fixed one exclude each other")
         if self.heads % self.kv_heads:
             raise ValueError(f"capped_attention: {self.heads} heads are not a multiple of {self.kv_heads} kv heads")
         if self.dim > 512:
@@ -70,23 +89,27 @@ class CappedAttention(Part):
         if self.position is not None and not (isinstance(self.position, Rotary) and self.position.layout == "half"):
             raise ValueError("capped_attention: the position encoding must be a rotary part with the half layout")
         self.own_kv = self.kv_heads if self.has_kv else 0
-        self.channels = (self.heads + self.own_kv) * self.dim + self.own_kv * self.vdim     # q | k | v
-        self.proj = self.o = self.filter = self.sinks = None
+        own_v = 0 if self.values_are_keys else self.own_kv
+        self.channels = (self.heads + self.own_kv) * self.dim + own_v * self.vdim     # q | k | v
+        self.proj = self.o = self.filter = self.sinks = self.q_norm = self.k_norm = None
 
     def wants(self):
         h, nh, nkv, d, vd = self.hidden_size, self.heads, self.kv_heads, self.dim, self.vdim
         w = {"q": TensorWant((nh * d, h)), "o": TensorWant((h, nh * vd))}
-        if self.has_kv:
-            w.update({"k": TensorWant((nkv * d, h)), "v": TensorWant((nkv * vd, h))})
+        kv = [("k", nkv * d)] if self.has_kv else []
+        if self.has_kv and not self.values_are_keys:
+            kv.append(("v", nkv * vd))
+        w.update({n: TensorWant((rows, h)) for n, rows in kv})
         if self.bias:
             w["q_bias"] = TensorWant((nh * d,), "vector")
-            if self.has_kv:
-                w.update({"k_bias": TensorWant((nkv * d,), "vector"), "v_bias": TensorWant((nkv * vd,), "vector")})
+            w.update({n + "_bias": TensorWant((rows,), "vector") for n, rows in kv})
         if self.taps:
             w["q_conv"] = TensorWant((nh * d, self.taps), "vector")
+            w.update({n + "_conv": TensorWant((rows, self.taps), "vector") for n, rows in kv})
+        if self.qk_norm_eps is not None:
+            w["q_norm"] = TensorWant((d,), "vector")
             if self.has_kv:
-                w.update({"k_conv": TensorWant((nkv * d, self.taps), "vector"),
-                          "v_conv": TensorWant((nkv * vd, self.taps), "vector")})
+                w["k_norm"] = TensorWant((d,), "vector")
         if self.gate:
             w["g"] = TensorWant((nh * vd, h))
         if self.sink:
@@ -94,7 +117,7 @@ class CappedAttention(Part):
         return w
 
     def load(self, t):
-        qkv = ["q", "k", "v"] if self.has_kv else ["q"]
+        qkv = (["q", "k"] if self.values_are_keys else ["q", "k", "v"]) if self.has_kv else ["q"]
         names = qkv + (["g"] if self.gate else [])
         bias = None
         if self.bias:
@@ -108,6 +131,11 @@ class CappedAttention(Part):
             self.filter = torch.cat([t[n + "_conv"] for n in qkv], dim=0).contiguous()
         if self.sink:
             self.sinks = t["sink"].to(torch.float32).contiguous()
+        elif self.fixed_sink is not None:
+            self.sinks = torch.full((self.heads,), self.fixed_sink, dtype=torch.float32, device=t["q"].device)
+        if self.qk_norm_eps is not None:
+            self.q_norm = t["q_norm"].to(torch.float32).contiguous()
+            self.k_norm = t["k_norm"].to(torch.float32).contiguous() if self.has_kv else None
 
     def kernel_units(self):
         return (kernels.gemm_units(self.compute) + kernels.attention_capped_units(self.compute, self.dim, self.vdim)
@@ -143,7 +171,10 @@ class CappedAttention(Part):
         q = torch.empty((t, nh * d), dtype=p.dtype, device=p.device)
         kernels.filter_rope_cache(p[:, :c], self.filter, filter_state, self.position.inv_freq(p.device) if rot else None, rot,
                                   ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, ctx.cu_seqlens, group.page_table, group.page_size,
-                                  q, kc if self.has_kv else None, vc if self.has_kv else None, nh, self.own_kv, d, vd)
+                                  q, kc if self.has_kv else None, vc if self.has_kv else None, nh, self.own_kv, d, vd,
+                                  q_norm=self.q_norm, k_norm=self.k_norm, norm_eps=self.qk_norm_eps or 0.0,
+                                  rot_magnitude=self.position.magnitude if rot else 1.0, q_temper=self.q_temper,
+                                  values_are_keys=self.values_are_keys)
         if self.taps > 1:
             kernels.short_filter_state(p[:, :c], filter_state, ctx.cu_seqlens, ctx.seq_slot, self.taps)
         att = torch.empty((t, nh * vd), dtype=p.dtype, device=p.device)

@@ -12,6 +12,14 @@ where l < original / high, becomes f / factor where l > original / low, and in b
 blend (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  The table is made
 once, in float64, and rounded to float32.
 
+A second form of ``scaling``, {"factor", "original", "fast", "slow"}, blends along the index
+instead of the wavelength: with d(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta) the
+index whose wavelength makes t turns over ``original`` positions, lo = max(floor(d(fast)), 0) and
+hi = min(ceil(d(slow)), rotary_dim - 1), the frequency is f / factor * r + f (1 - r) with
+r = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), and the cosines and sines are multiplied by
+``magnitude`` = 0.1 ln(factor) + 1 (1 without this form).  Only kernels that take a magnitude can
+use such a part (``capped_attention`` does; the fused kernels of ``attention`` do not).
+
 The attention part fuses the "half" rotation into its q/k kernel when its position encoding is
 this class, and the latent attention part the "interleaved" one into the kernel that writes its
 cache rows; ``apply`` is the stand-alone form of either."""
@@ -41,7 +49,10 @@ class Rotary(Part):
         i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
         freq = 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64), 2.0 * i / max(self.rotary_dim, 1))
         self.scaling = spec.params.get("scaling")
-        if self.scaling:
+        self.magnitude = 1.0
+        if self.scaling and ("fast" in self.scaling or "slow" in self.scaling):
+            freq, self.magnitude = self.ramped(freq, self.scaling, self.rotary_dim, self.theta)
+        elif self.scaling:
             freq = self.scaled(freq, self.scaling)
         self._inv_freq_host = freq.to(torch.float32)
         self._inv_freq = {}
@@ -64,6 +75,25 @@ class Rotary(Part):
         out = torch.where(wavelength > original / low, freq / factor, blend)
         return torch.where(wavelength < original / high, freq, out)
 
+    @staticmethod
+    def ramped(freq: torch.Tensor, scaling: dict, dims: int, theta: float):
+        """(``freq`` (float64) blended towards freq / factor along the index, the magnitude)."""
+        try:
+            factor, original, fast, slow = (float(scaling[k]) for k in ("factor", "original", "fast", "slow"))
+        except (KeyError, TypeError, ValueError):
+            raise ValueError(f"rotary: scaling needs the numbers factor, original, fast and slow, got {scaling!r}") from None
+        if factor <= 0 or original <= 0 or fast <= 0 or slow <= 0 or theta <= 1.0:
+            raise ValueError(f"rotary: scaling factor, original, fast and slow must be positive, got {scaling!r}")
+
+        def index_of(turns):
+            return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+        lo = max(math.floor(index_of(fast)), 0)
+        hi = min(math.ceil(index_of(slow)), dims - 1)
+        i = torch.arange(freq.numel(), dtype=torch.float64)
+        ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return freq / factor * ramp + freq * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
     def inv_freq(self, device) -> torch.Tensor:
         t = self._inv_freq.get(device)
         if t is None:
@@ -76,7 +106,7 @@ class Rotary(Part):
     def table(self, ctx) -> torch.Tensor:
         """(cos, sin) of the step's packed tokens' angles, [tokens, rotary_dim / 2, 2] float32,
         computed once a step and shared by every layer with the same rotation."""
-        assert self.layout == "half"
+        assert self.layout == "half" and self.magnitude == 1.0
         key = ("rope_table", self.rotary_dim, self.theta, repr(self.scaling))
         t = ctx.extras.get(key)
         if t is None:
@@ -85,6 +115,8 @@ class Rotary(Part):
 
     def apply(self, ctx, q, k):
         """Rotates q [T, nh, hd] and k [T, nkv, hd] (contiguous views) in place."""
+        if self.magnitude != 1.0:
+            raise ValueError("rotary: the stand-alone rotation takes no magnitude (use a mixer whose kernel does)")
         for x in (q, k):
             t, heads, hd = x.shape
             if self.layout == "interleaved":
