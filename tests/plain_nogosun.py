@@ -140,8 +140,9 @@ def tempered_attention_mixer(h, P, m, eps):
     q = rms_norm((h @ P["q"].T + P["q.b"]).reshape(T, H, D), P["q.norm"], eps)
     k = rms_norm((h @ P["k"].T + P["k.b"]).reshape(T, G, D), P["k.norm"], eps)
     v = (h @ P["v"].T + P["v.b"]).reshape(T, G, Vd)
-    q = q * query_temperature(T, m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
-    o = masked_attention(q, k, v, m["scale"], cap=m["softcap"], plus_one=True)
+    if m.get("q_temp"):
+        q = q * query_temperature(T, m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
+    o = masked_attention(q, k, v, m["scale"], cap=m.get("softcap") or 0.0, plus_one=True)
     return (o.reshape(T, H * Vd) * sigmoid(h @ P["g"].T)) @ P["o"].T
 
 

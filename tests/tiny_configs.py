@@ -239,3 +239,89 @@ DALERAX_C = {
         {"type": "wkv", "mixer": {"heads": 2, "dim": 12, "rank": 3}, "mlp": None},
     ],
 }
+
+
+# ---------------------------------------------------------------------------------------------- Nogosun
+def _nogosun_moe(experts, top, ff):
+    return {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
+
+
+def _nogosun_attention(heads, kv_heads, dim, scale, size=None, keep_first=None, base=1e4, dims=0, scaling=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": scale}
+    if size is not None:
+        m["mask"] = {"size": size} if keep_first is None else {"size": size, "keep_first": keep_first}
+    if dims is not None:
+        m["rot"] = {"base": base, "dims": dims, "scaling": None if scaling is None else dict(
+            zip(("factor", "original", "fast", "slow"), scaling))}
+    return m
+
+
+def _nogosun_delta(heads, kv_heads, dim, vdim, conv, decay_rank, gate_rank):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "decay_rank": decay_rank,
+            "gate_rank": gate_rank}
+
+
+def _nogosun_pair(left, right, left_scale, right_scale):
+    lh, lg, ld, lv, lscale, cap, temp = left
+    rh, rd, rv, tau, rank = right
+    lm = {"heads": lh, "kv_heads": lg, "dim": ld, "vdim": lv, "scale": lscale}
+    if cap is not None:
+        lm["softcap"] = cap
+    if temp is not None:
+        lm["q_temp"] = {"coef": temp[0], "every": temp[1]}
+    return {"left": lm, "right": {"heads": rh, "dim": rd, "vdim": rv, "tau": tau, "rank": rank},
+            "left_scale": left_scale, "right_scale": right_scale}
+
+
+_NA_ATT = _nogosun_attention(4, 2, 32, 0.2, 20, 3, 3000.0, 8, (4.0, 16, 2.0, 0.5))
+_NA_PAIR = _nogosun_pair((4, 2, 16, 24, 0.3, 25.0, (1.5, 7)), (3, 8, 24, 5.0, 6), 1.6, 0.9)
+_NA_MOE = _nogosun_moe(5, 2, 40)
+
+# Small sizes that no kernel of the tensor cores takes for attention but the products do (a width of
+# 72): a two-branch layer first and again later with the same tensors, a window of 20 beside 3 kept
+# tokens run twice (the second time with a cache of its own), fewer q/k heads than heads in the delta
+# rule, a filter of 4 taps, a temperature that changes every 7 positions, a layer without feed-forward.
+NOGOSUN_A = {
+    "architecture": "Nogosun", "vocab": 211, "width": 72, "embedding": {"scale": 3.0}, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "parallel", "mixer": _NA_PAIR, "mlp": _NA_MOE},
+        {"type": "attention", "mixer": _NA_ATT, "mlp": _nogosun_moe(4, 4, 32)},
+        {"type": "channel_delta", "mixer": _nogosun_delta(4, 2, 24, 16, 4, 6, 5), "mlp": None},
+        {"type": "attention", "mixer": _NA_ATT, "mlp": _nogosun_moe(4, 4, 32), "weights_of": 1},
+        {"type": "parallel", "mixer": _NA_PAIR, "mlp": _NA_MOE, "weights_of": 0},
+        {"type": "channel_delta", "mixer": _nogosun_delta(2, 2, 40, 8, 2, 3, 9), "mlp": _nogosun_moe(3, 1, 48)},
+    ],
+}
+
+_NB_DELTA = _nogosun_delta(4, 1, 128, 64, 3, 16, 8)
+
+# Sizes the tensor cores take: keys of 64 under a window of 130 beside 70 kept tokens (more than a
+# page of them), every dim rotated without scaling; tempered attention with keys of 64 and values of
+# 128 beside gated linear attention of heads of 64; a delta rule with one q/k head of 128 for four
+# heads, run twice; eight experts of which three are chosen.
+NOGOSUN_B = {
+    "architecture": "Nogosun", "vocab": 520, "width": 128, "embedding": {"scale": 11.3}, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "channel_delta", "mixer": _NB_DELTA, "mlp": _nogosun_moe(8, 3, 64)},
+        {"type": "attention", "mixer": _nogosun_attention(8, 4, 64, 0.125, 130, 70, 250000.0, 64), "mlp": _nogosun_moe(8, 3, 64)},
+        {"type": "parallel", "mixer": _nogosun_pair((4, 2, 64, 128, 0.125, 30.0, (0.5, 50)), (2, 64, 64, 16.0, 16), 0.8, 0.5),
+         "mlp": _nogosun_moe(6, 2, 96)},
+        {"type": "channel_delta", "mixer": _NB_DELTA, "mlp": _nogosun_moe(8, 3, 64), "weights_of": 0},
+        {"type": "attention", "mixer": _nogosun_attention(2, 1, 128, 0.09, 64, 0, 1000.0, 32, (8.0, 64, 4.0, 1.0)),
+         "mlp": None},
+    ],
+}
+
+# A width that is no multiple of 8 and heads that are no multiple of 16 (plain kernels throughout in
+# bfloat16): attention without a window and without rotation, a window of 17 with nothing kept (a
+# ring of pages), a filter of one tap, no cap and no temperature, every expert chosen, tau of one.
+NOGOSUN_C = {
+    "architecture": "Nogosun", "vocab": 97, "width": 52, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "attention", "mixer": _nogosun_attention(2, 2, 20, 0.22, None, None, 50.0, None), "mlp": _nogosun_moe(2, 2, 20)},
+        {"type": "channel_delta", "mixer": _nogosun_delta(2, 1, 12, 20, 1, 2, 1), "mlp": None},
+        {"type": "parallel", "mixer": _nogosun_pair((2, 1, 12, 20, 0.3, None, None), (1, 20, 12, 1.0, 3), 1.0, 1.0),
+         "mlp": _nogosun_moe(3, 1, 12)},
+        {"type": "attention", "mixer": _nogosun_attention(3, 1, 12, 0.3, 17, None, 50.0, 4), "mlp": _nogosun_moe(2, 1, 28)},
+    ],
+}
