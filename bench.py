@@ -2,7 +2,7 @@
 """Decode and prefill throughput of Qwen3-shaped models with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference] [--config 8b|4b|32b]
-    python bench.py --compare toretar|kuporax|dalerax [--sizes small,lite,mid] [--batch 8] [--context 4096]
+    python bench.py --compare toretar|kuporax|dalerax|nogosun [--sizes small,lite,mid] [--batch 8] [--context 4096]
 
 ``--config 8b`` (the default) is the headline benchmark.  A step is one decode step of a batch
 of 8 sequences at a context of 8,192 tokens.  One JSON line is printed: ``value`` = decoded
@@ -244,6 +244,55 @@ def dalerax_cache_bytes(cfg, lengths, element_size=2):
     return total
 
 
+def nogosun_prefill_flops(cfg, t):
+    """Floating-point operations of a prompt of ``t`` tokens from position 0: every product (a layer
+    that runs another layer's tensors counts like one of its own), the scores and weighted values over
+    the keys each token's mask lets it see, the two-matrix projections, the recurrences as they are
+    written (delta rule: 6 dim vdim a head and token; gated linear attention: 4 dim vdim), the router
+    and the chosen experts (two matrices each)."""
+    w, total = cfg["width"], 0
+    for layer in cfg["layers"]:
+        m, pairs = layer["mixer"], 0
+        if layer["type"] == "attention":
+            per_token = 2 * w * (m["heads"] + m["kv_heads"]) * m["dim"] + 2 * m["heads"] * m["vdim"] * w
+            mask = m.get("mask")
+            seen = sum(_dalerax_seen(mask, p) for p in range(t)) if mask else t * (t + 1) // 2
+            pairs = 2 * m["heads"] * (m["dim"] + m["vdim"]) * seen
+        elif layer["type"] == "channel_delta":
+            qk, hv, hd = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"], m["heads"] * m["dim"]
+            ra, rg = m.get("decay_rank", 16), m.get("gate_rank", 16)
+            per_token = (2 * w * (2 * qk + hv + m["heads"] + ra + rg) + 2 * (ra * hd + rg * hv) + 2 * hv * w
+                         + 6 * m["heads"] * m["dim"] * m["vdim"])
+        else:
+            a, r = m["left"], m["right"]
+            per_token = (2 * w * ((a["heads"] + a["kv_heads"]) * a["dim"] + (a["kv_heads"] + a["heads"]) * a["vdim"])
+                         + 2 * a["heads"] * a["vdim"] * w)
+            pairs = 2 * a["heads"] * (a["dim"] + a["vdim"]) * (t * (t + 1) // 2)
+            hd, hv, rank = r["heads"] * r["dim"], r["heads"] * r["vdim"], r.get("rank", 16)
+            per_token += 2 * w * (2 * hd + 2 * hv + rank) + 2 * rank * hd + 2 * hv * w + 4 * r["heads"] * r["dim"] * r["vdim"]
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            per_token += 2 * w * mlp["router"]["experts"] + 4 * w * mlp["router"]["top"] * mlp["expert"]["ff"]
+        total += per_token * t + pairs
+    return total + 2 * w * cfg["vocab"]
+
+
+def nogosun_cache_bytes(cfg, lengths, element_size=2):
+    """Bytes of cached keys and values one decode step reads: what each attention's mask sees (every
+    key for the two-branch layer's attention); values that are the keys are cached, and read, as values too."""
+    total = 0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "parallel":
+            m = m["left"]
+        elif layer["type"] != "attention":
+            continue
+        per_key = m["kv_heads"] * (m["dim"] + m["vdim"]) * element_size
+        mask = m.get("mask")
+        total += sum(per_key * (_dalerax_seen(mask, n - 1) if mask else n) for n in lengths)
+    return total
+
+
 def fill_cache(runner, slots, length, real, vocab, gen):
     """Brings every slot to ``length`` cached tokens: by running prompts (real) or by
     reserving the pages and writing random keys and values (synthetic)."""
@@ -302,8 +351,8 @@ def time_decode(eng, batch, ctx_end, steps, warmup, real_fill, hbm_gbs, cfg=None
     ms = e0.elapsed_time(e1) / steps
     clock_rec = clocks.stop()
     lengths = [runner.length(s) for s in slots]
-    masked = cfg is not None and cfg.get("architecture") == "Dalerax"
-    nbytes = decode_bytes(eng.model, runner, lengths, dalerax_cache_bytes(cfg, lengths) if masked else None)
+    masked = {"Dalerax": dalerax_cache_bytes, "Nogosun": nogosun_cache_bytes}.get(cfg.get("architecture")) if cfg else None
+    nbytes = decode_bytes(eng.model, runner, lengths, masked(cfg, lengths) if masked else None)
     for s in slots:
         runner.close(s)
     kernels.check_status()
@@ -337,6 +386,8 @@ def time_prefill(eng, cfg, tokens, tflops, tflops_sustained):
         flops = kuporax_prefill_flops(cfg, tokens)
     elif cfg.get("architecture") == "Dalerax":
         flops = dalerax_prefill_flops(cfg, tokens)
+    elif cfg.get("architecture") == "Nogosun":
+        flops = nogosun_prefill_flops(cfg, tokens)
     elif cfg.get("sliding_window") and cfg.get("use_sliding_window"):
         size = cfg["sliding_window"]      # a window on every layer: the keys a token sees, not the causal half
         seen = sum(min(p + 1, size) for p in range(tokens))
@@ -529,10 +580,10 @@ def kernel_table(eng, tokens, batch, context):
 def run_compare(args):
     """Prompt and decode throughput of models of one architecture beside models of another with the
     same width, depth and per-token feed-forward size (Toretar and Kuporax beside Qwen3, Dalerax
-    beside Kuporax), with a table of each one's kernels."""
-    from gemmars_b200.tuning import DALERAX_PAIRS, KUPORAX_PAIRS, PAIRS
-    pairs = {"kuporax": KUPORAX_PAIRS, "dalerax": DALERAX_PAIRS}.get(args.compare, PAIRS)
-    beside = "kuporax" if args.compare == "dalerax" else "qwen3"
+    beside Kuporax, Nogosun beside Dalerax), with a table of each one's kernels."""
+    from gemmars_b200.tuning import DALERAX_PAIRS, KUPORAX_PAIRS, NOGOSUN_PAIRS, PAIRS
+    pairs = {"kuporax": KUPORAX_PAIRS, "dalerax": DALERAX_PAIRS, "nogosun": NOGOSUN_PAIRS}.get(args.compare, PAIRS)
+    beside = {"dalerax": "kuporax", "nogosun": "dalerax"}.get(args.compare, "qwen3")
     hbm_gbs, tflops, tflops_sustained, peak_src = peaks()
     sizes = [s for s in args.sizes.split(",") if s]
     out = {}
@@ -571,8 +622,9 @@ def main():
     ap.add_argument("--e2e-tokens", type=int, default=E2E_TOKENS,
                     help="tokens a sequence generates in the end-to-end run (fewer for runs under a profiler)")
     ap.add_argument("--options", default="", help='further engine options, "key=value;key=value"')
-    ap.add_argument("--compare", choices=["toretar", "kuporax", "dalerax"], default=None,
-                    help="instead of the headline: models of that architecture beside ones of equal size (Qwen3-shaped; Kuporax-shaped for dalerax)")
+    ap.add_argument("--compare", choices=["toretar", "kuporax", "dalerax", "nogosun"], default=None,
+                    help="instead of the headline: models of that architecture beside ones of equal size (Qwen3-shaped; "
+                         "Kuporax-shaped for dalerax; Dalerax-shaped for nogosun)")
     ap.add_argument("--sizes", default="small,lite,mid", help="with --compare: which pairs of tuning.PAIRS")
     args = ap.parse_args()
     if args.impl == "reference":

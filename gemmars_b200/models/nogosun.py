@@ -63,6 +63,8 @@ def _num(problems, where, obj, name, kind=int, allow_zero=False, optional=False)
     v = obj.get(name) if isinstance(obj, dict) else None
     if v is None and optional:
         return None
+    if kind is int and isinstance(v, float) and v.is_integer():
+        v = int(v)                                   # a count written as 256.0
     ok = isinstance(v, int) and not isinstance(v, bool) if kind is int else (
         isinstance(v, (int, float)) and not isinstance(v, bool))
     if not ok:

@@ -150,6 +150,50 @@ for _name, (_d, _k) in DALERAX_PAIRS.items():
     PAIR_SHAPES[f"dalerax-{_name}"] = (f"Dalerax shape '{_name}'", _d)
 
 
+def nogosun_shape(width, ff, heads, window, experts, top, order=("channel_delta", "parallel", "attention", "attention"),
+                  vocab=102400):
+    """A Nogosun config.json object: attention layers of ``heads`` heads of 128 whose values are their
+    keys (a quarter as many kv heads, four kept first tokens, half of every head rotated with
+    scaling), the second of which runs the first one's tensors again; a delta rule with a decay per
+    key channel, ``heads`` heads of 128 over half as many q/k heads, a filter of 4 taps, inner sizes
+    of 64; a two-branch layer of tempered attention (half the heads, over every key) beside gated
+    linear attention (half the heads, keys of 64 and values of 128).  Every layer routes ``top`` of
+    ``experts`` experts without gates, sized so that a token passes ``ff`` hidden units in all."""
+    rot = {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // top}}
+    half = max(1, heads // 2)
+    mixers = {
+        "channel_delta": {"heads": heads, "kv_heads": half, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64},
+        "parallel": {"left": {"heads": half, "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                              "softcap": 50.0, "q_temp": {"coef": 0.5, "every": 256}},
+                     "right": {"heads": half, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 64},
+                     "left_scale": 1.0, "right_scale": 1.0},
+        "attention": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                      "mask": {"size": window, "keep_first": 4}, "rot": rot},
+    }
+    layers, first = [], {}
+    for i, kind in enumerate(order):
+        layer = {"type": kind, "mixer": mixers[kind], "mlp": mlp}
+        if kind == "attention" and kind in first:
+            layer["weights_of"] = first[kind]
+        first.setdefault(kind, i)
+        layers.append(layer)
+    return {"architecture": "Nogosun", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": layers}
+
+
+# Nogosun beside Dalerax, the nearest design the package has (parallel blocks, kept first tokens beside a
+# window, a recurrence with a decay per key channel, routed experts): the same width, depth,
+# vocabulary, heads, window, experts and hidden units a token passes
+NOGOSUN_PAIRS = {
+    "small": (nogosun_shape(1024, 4096, 8, 512, 16, 4), dalerax_shape(1024, 4096, 8, 512, 16, 3)),
+    "lite": (nogosun_shape(2048, 8192, 16, 1024, 32, 4), dalerax_shape(2048, 8192, 16, 1024, 32, 6)),
+    "mid": (nogosun_shape(4096, 12288, 32, 2048, 32, 4), dalerax_shape(4096, 12288, 32, 2048, 32, 6)),
+}
+for _name, (_n, _d) in NOGOSUN_PAIRS.items():
+    PAIR_SHAPES[f"nogosun-{_name}"] = (f"Nogosun shape '{_name}'", _n)
+
+
 def random_engine(cfg, max_batch, cache_tokens, options=""):
     """An engine over random weights of ``cfg`` made on the device; the tensors are taken out of
     their dict as they are bound, so that a model of 65 GB and its stacked q/k/v and gate/up copies
