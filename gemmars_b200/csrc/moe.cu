@@ -86,14 +86,6 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
   for (int e = lane; e < E; e += 32) z[e] = zin[(size_t)t * ldz + e] + (bias ? bias[e] : 0.f);
   if (has_gate && lane == 0) sg[t] = 1.0f / (1.0f + expf(-zin[(size_t)t * ldz + E]));
   __syncwarp();
-  float total = 0.f;               // all_softmax: the sum of exp(z - max) over every expert, in index order per lane
-  if (all_softmax) {
-    float top1 = -INFINITY;
-    for (int e = lane; e < E; e += 32) top1 = fmaxf(top1, z[e]);
-    top1 = warp_max(top1);
-    for (int e = lane; e < E; e += 32) total += expf(z[e] - top1);
-    total = warp_sum(total);
-  }
   float mine = 0.f, first = 0.f;   // lane k keeps the k-th chosen logit
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
@@ -117,8 +109,13 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
     __syncwarp();
   }
   const float e = lane < top ? expf(mine - first) : 0.f;
-  const float sum = warp_sum(e);
-  if (lane < top) wts[(size_t)t * top + lane] = e / (all_softmax ? total : sum);
+  float sum = warp_sum(e);
+  if (all_softmax) {               // the experts not chosen join the denominator (the chosen ones' places hold -inf: nothing)
+    float rest = 0.f;
+    for (int i = lane; i < E; i += 32) rest += expf(z[i] - first);
+    sum += warp_sum(rest);
+  }
+  if (lane < top) wts[(size_t)t * top + lane] = e / sum;
 }
 
 // ---- gate and up of one (token, slot): FEATS features a block, a warp per feature in turn

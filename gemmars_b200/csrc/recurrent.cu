@@ -537,9 +537,9 @@ __global__ void __launch_bounds__(128) gated_group_norm_kernel(const float* __re
   }
 }
 
-// The same for groups of at most 64 channels: a warp a group (eight groups a block), the sum by
-// shuffles, so that a token's row is not cut into blocks of one or two warps.
-template <typename O>
+// The same for groups of at most 32 E channels (E = 2 or 4): a warp a group (eight groups a block),
+// the sum by shuffles, so that a token's row is not cut into blocks of one or two warps.
+template <typename O, int E>
 __global__ void __launch_bounds__(256) gated_group_norm_warp_kernel(const float* __restrict__ y, const float* __restrict__ gate,
                                                                    long long ldgate, const float* __restrict__ w, int wn,
                                                                    O* __restrict__ out, int n, int gs, float eps, int gate_first,
@@ -551,9 +551,9 @@ __global__ void __launch_bounds__(256) gated_group_norm_warp_kernel(const float*
   const int base = group * gs;
   const float* row = y + (size_t)t * n + base;
   const float* grow = gate + (size_t)t * ldgate + base;
-  float val[2], gt[2], ss = 0.f;
+  float val[E], gt[E], ss = 0.f;
 #pragma unroll
-  for (int e = 0; e < 2; ++e) {
+  for (int e = 0; e < E; ++e) {
     const int i = lane + 32 * e;
     val[e] = i < gs ? row[i] : 0.f;
     gt[e] = i < gs ? gate_f(grow[i], gate_act) : 0.f;
@@ -563,7 +563,7 @@ __global__ void __launch_bounds__(256) gated_group_norm_warp_kernel(const float*
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)gs + eps);
 #pragma unroll
-  for (int e = 0; e < 2; ++e) {
+  for (int e = 0; e < E; ++e) {
     const int i = lane + 32 * e;
     if (i >= gs) continue;
     const float res = gate_first ? val[e] * inv * w[(base + i) % wn] : val[e] * inv * w[(base + i) % wn] * gt[e];
@@ -577,14 +577,14 @@ GB_EXPORT int gb_gated_group_norm_act(const float* y, const float* gate, long lo
   if (ntok <= 0) return 0;
   if (gs <= 0 || n % gs || wn <= 0) return GB_ERR_SIZE;
   if (out_dtype != GB_F32 && out_dtype != GB_BF16) return GB_ERR_DTYPE;
-  if (gs <= 64) {
+  if (gs <= 128) {
     dim3 wgrid(ntok, (n / gs + 7) / 8);
-    if (out_dtype == GB_F32)
-      gb_launch(gated_group_norm_warp_kernel<float>, wgrid, 256, 0, stream, y, gate, ldgate, w, wn, (float*)out, n, gs, eps,
-                gate_first, out_scale, gate_act);
-    else
-      gb_launch(gated_group_norm_warp_kernel<bf16>, wgrid, 256, 0, stream, y, gate, ldgate, w, wn, (bf16*)out, n, gs, eps,
-                gate_first, out_scale, gate_act);
+#define GB_NORM_WARP(O, E)                                                                                              \
+  gb_launch(gated_group_norm_warp_kernel<O, E>, wgrid, 256, 0, stream, y, gate, ldgate, w, wn, (O*)out, n, gs, eps, gate_first, \
+            out_scale, gate_act)
+    if (out_dtype == GB_F32) { if (gs <= 64) GB_NORM_WARP(float, 2); else GB_NORM_WARP(float, 4); }
+    else { if (gs <= 64) GB_NORM_WARP(bf16, 2); else GB_NORM_WARP(bf16, 4); }
+#undef GB_NORM_WARP
     return gb_launch_status();
   }
   dim3 grid(ntok, n / gs);
