@@ -2,7 +2,7 @@
 
 A decoder of parallel blocks with two RMS norms a layer: x += mixer(norm1(x)) + ffn(norm2(x)), both
 norms of the same x, weights as stored.  The configuration lists the layers one by one; a layer with
-``weights_of: j`` runs layer j's tensors again with a cache and state of its own.  Three mixers:
+``weights_of: j`` runs layer j's tensors (j before or after it) with a cache and state of its own.  Three mixers:
 
 * ``attention``: grouped-query softmax attention whose values are its keys as projected (no value
   matrix), biases on q and k, the first ``rot.dims`` dims of every head rotated in the half layout
@@ -185,10 +185,21 @@ class NogosunConfig(ModelConfig):
                 _check_mlp(p, w + ".mlp", layer["mlp"])
             if "weights_of" in layer:
                 j = layer["weights_of"]
-                if not isinstance(j, int) or isinstance(j, bool) or not 0 <= j < i or not isinstance(layers[j], dict):
-                    p.append(f"{w}.weights_of: {j!r} is not a layer before this one")
+                if (not isinstance(j, int) or isinstance(j, bool) or not 0 <= j < len(layers) or j == i
+                        or not isinstance(layers[j], dict)):
+                    p.append(f"{w}.weights_of: {j!r} is not another layer")
                 elif layers[j].get("type") != kind:
                     p.append(f"{w}.weights_of: layer {j} is a {layers[j].get('type')!r} layer, this one {kind!r}")
+                else:
+                    seen, at = {i}, j            # the chain of owners must end at a layer with tensors of its own
+                    while isinstance(layers[at], dict) and "weights_of" in layers[at] and at not in seen:
+                        seen.add(at)
+                        nxt = layers[at]["weights_of"]
+                        if not isinstance(nxt, int) or isinstance(nxt, bool) or not 0 <= nxt < len(layers):
+                            break
+                        at = nxt
+                    if isinstance(layers[at], dict) and "weights_of" in layers[at]:
+                        p.append(f"{w}.weights_of: the layers that share tensors name one another in a circle")
         if p:
             raise ConfigError("config.json: " + "; ".join(p))
         return cls(vocab=vocab, width=width, embedding_scale=emb, norm_eps=eps, layers=tuple(layers))
@@ -276,10 +287,9 @@ def build_plan(cfg: NogosunConfig, names=None) -> ModelPlan:
     def norm(name):
         return PartSpec("rmsnorm", {"size": cfg.width, "eps": cfg.norm_eps}, {"weight": name})
 
-    layers, schedule, place, ignored = [], [], {}, []
+    layers, place, ignored = [], {}, []
     for i, layer in enumerate(cfg.layers):
         if "weights_of" in layer:
-            schedule.append(ScheduleEntry(place[owner(cfg, i)]))
             continue
         m, prefix = layer["mixer"], f"l{i}.mix."
         if layer["type"] == "attention":
@@ -296,7 +306,8 @@ def build_plan(cfg: NogosunConfig, names=None) -> ModelPlan:
             ignored.append(f"l{i}.norm2")          # a layer without feed-forward has no use for its second norm
         place[i] = len(layers)
         layers.append(LayerSpec(parts, "parallel"))
-        schedule.append(ScheduleEntry(place[i]))
+    # every run of a layer, with tensors of its own or another layer's (named before or after it), keeps its own cache
+    schedule = [ScheduleEntry(place[owner(cfg, i)]) for i in range(len(cfg.layers))]
     plan = ModelPlan(
         hidden_size=cfg.width, vocab_size=cfg.vocab,
         embedding=PartSpec("embedding", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "scale": cfg.embedding_scale},

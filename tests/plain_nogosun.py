@@ -267,7 +267,9 @@ def forward(config, tensors, tokens, return_layers=False):
     x = tensors["embed"][tokens] * config["embedding"]["scale"]
     layers = []
     for i, layer in enumerate(config["layers"]):
-        src = layer.get("weights_of", i)
+        src = i
+        while "weights_of" in config["layers"][src]:          # the layer whose tensors this one runs
+            src = config["layers"][src]["weights_of"]
         y = MIXERS[layer["type"]](rms_norm(x, tensors[f"l{src}.norm1"], eps), sub(tensors, f"l{src}.mix."), layer["mixer"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:

@@ -42,6 +42,32 @@ def test_configuration_reports_every_problem_at_once():
         NogosunConfig.from_dict(bad)
     for piece in ("right.tau", "q_temp.every", "left_scale"):
         assert piece in str(e.value), piece
+    circle = copy.deepcopy(NOGOSUN_A)
+    circle["layers"][1]["weights_of"] = 3                           # 1 -> 3 -> 1
+    with pytest.raises(ConfigError) as e:
+        NogosunConfig.from_dict(circle)
+    assert "circle" in str(e.value)
+
+
+def test_a_layer_may_run_the_tensors_of_a_later_layer():
+    """The owner of shared tensors need not come first: here the first layer runs the last one's."""
+    from gemmars_b200.config.registry import resolve_architecture
+    from gemmars_b200.engine.model import DecoderModel
+    from gemmars_b200.weights import random_weights
+    raw = copy.deepcopy(NOGOSUN_C)
+    raw["layers"].insert(0, dict(copy.deepcopy(raw["layers"][3]), weights_of=4))
+    arch = resolve_architecture(raw)
+    cfg = arch.config_class.from_dict(raw)
+    model = DecoderModel(arch.build_plan(cfg, None), "float32", "cpu")
+    assert [e.layer for e in model.plan.schedule] == [3, 0, 1, 2, 3] and len(model.blocks) == 4
+    assert not any(name.startswith("l0.") for name in model.expected_tensors())
+    w = {k: v.double().numpy() for k, v in random_weights(raw, 2).items()}
+    toks = list(range(20))
+    copies = dict(w)
+    copies.update({"l0." + k[len("l4."):]: v for k, v in w.items() if k.startswith("l4.")})
+    own = copy.deepcopy(raw)
+    del own["layers"][0]["weights_of"]
+    assert np.allclose(plain.forward(raw, w, toks), plain.forward(own, copies, toks), rtol=0, atol=1e-12)
 
 
 @pytest.mark.parametrize("raw", [NOGOSUN_A, NOGOSUN_B, NOGOSUN_C], ids="ABC")
