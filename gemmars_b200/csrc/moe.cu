@@ -8,7 +8,7 @@
 //
 // Two more forms for designs that ask for them: `all_softmax` (the weights are the chosen experts'
 // shares of the softmax over ALL experts, not renormalized), and experts without a gate
-// (`gated` 0: y = gelu(up h) with the exact, erf form; out = down y; w_gu then is [E, ff, width]).
+// (gb_moe_up: y = gelu(up h) with the exact, erf form; out = down y; the first matrices are [E, ff, width]).
 //
 // The router's logits are a product like any other (the part computes them in float32); this unit
 // picks the experts from them and runs the experts token-major: a block owns one (token, chosen

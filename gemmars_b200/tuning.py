@@ -159,14 +159,14 @@ def nogosun_shape(width, ff, heads, window, experts, top, order=("channel_delta"
     of 64; a two-branch layer of tempered attention (half the heads, over every key) beside gated
     linear attention (half the heads, keys of 64 and values of 128).  Every layer routes ``top`` of
     ``experts`` experts without gates, sized so that a token passes ``ff`` hidden units in all."""
-    rot = {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}
+    rot = {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 8192, "fast": 16.0, "slow": 2.0}}
     mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // top}}
     half = max(1, heads // 2)
     mixers = {
         "channel_delta": {"heads": heads, "kv_heads": half, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64},
         "parallel": {"left": {"heads": half, "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
-                              "softcap": 50.0, "q_temp": {"coef": 0.5, "every": 256}},
-                     "right": {"heads": half, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 64},
+                              "softcap": 30.0, "q_temp": {"coef": 0.25, "every": 512}},
+                     "right": {"heads": half, "dim": 64, "vdim": 128, "tau": 8.0, "rank": 64},
                      "left_scale": 1.0, "right_scale": 1.0},
         "attention": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
                       "mask": {"size": window, "keep_first": 4}, "rot": rot},

@@ -303,11 +303,11 @@ NOGOSUN_B = {
     "architecture": "Nogosun", "vocab": 520, "width": 128, "embedding": {"scale": 11.3}, "norm": {"eps": 1e-6},
     "layers": [
         {"type": "channel_delta", "mixer": _NB_DELTA, "mlp": _nogosun_moe(8, 3, 64)},
-        {"type": "attention", "mixer": _nogosun_attention(8, 4, 64, 0.125, 130, 70, 250000.0, 64), "mlp": _nogosun_moe(8, 3, 64)},
-        {"type": "parallel", "mixer": _nogosun_pair((4, 2, 64, 128, 0.125, 30.0, (0.5, 50)), (2, 64, 64, 16.0, 16), 0.8, 0.5),
+        {"type": "attention", "mixer": _nogosun_attention(8, 4, 64, 0.125, 130, 70, 500000.0, 64), "mlp": _nogosun_moe(8, 3, 64)},
+        {"type": "parallel", "mixer": _nogosun_pair((4, 2, 64, 128, 0.125, 30.0, (0.4, 50)), (2, 64, 64, 12.0, 16), 0.7, 0.6),
          "mlp": _nogosun_moe(6, 2, 96)},
         {"type": "channel_delta", "mixer": _NB_DELTA, "mlp": _nogosun_moe(8, 3, 64), "weights_of": 0},
-        {"type": "attention", "mixer": _nogosun_attention(2, 1, 128, 0.09, 64, 0, 1000.0, 32, (8.0, 64, 4.0, 1.0)),
+        {"type": "attention", "mixer": _nogosun_attention(2, 1, 128, 0.09, 64, 0, 1000.0, 32, (6.0, 64, 4.0, 2.0)),
          "mlp": None},
     ],
 }
