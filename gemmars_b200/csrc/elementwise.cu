@@ -65,9 +65,12 @@ GB_EXPORT int gb_embed_gather(const void* table, int table_dtype, const int* tok
 // ------------------------------------------------------------------ RMSNorm
 // out[r, :] = x[src(r), :] * (mean(x^2) + eps)^-1/2 * w, statistics in float32.
 // rows_index (optional) gathers: src(r) = rows_index[r].
+// w2, out2 (optional): a second norm of the same rows with the same eps, which shares the statistics:
+// out2[r, :] = x[src(r), :] * (mean(x^2) + eps)^-1/2 * w2, made in the same pass.
 template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ out,
-                               const int* __restrict__ rows_index, int n, float eps) {
+                               const int* __restrict__ rows_index, int n, float eps, const float* __restrict__ w2,
+                               T* __restrict__ out2) {
   __shared__ float scratch[33];
   pdl_release_next();
   constexpr int KEEP = 4;            // float4s a thread keeps in registers between the two passes
@@ -117,6 +120,17 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
         __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
         ((uint2*)o)[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
       }
+      if (out2) {
+        const float4 g2 = ((const float4*)w2)[i];
+        T* o2 = out2 + (size_t)r * n;
+        const float a2 = v.x * inv * g2.x, b2 = v.y * inv * g2.y, c2 = v.z * inv * g2.z, d2 = v.w * inv * g2.w;
+        if (sizeof(T) == 4) {
+          ((float4*)o2)[i] = make_float4(a2, b2, c2, d2);
+        } else {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(a2, b2), hi = __floats2bfloat162_rn(c2, d2);
+          ((uint2*)o2)[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+        }
+      }
     }
     return;
   }
@@ -124,7 +138,10 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < n; i += blockDim.x) ss += row[i] * row[i];
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)n + eps);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<T>(row[i] * inv * w[i]);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    o[i] = from_f32<T>(row[i] * inv * w[i]);
+    if (out2) out2[(size_t)r * n + i] = from_f32<T>(row[i] * inv * w2[i]);
+  }
 }
 
 // Many rows (a prompt), bfloat16 out: one warp per row, no block barrier.  The row is read twice
@@ -133,7 +150,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 // for every number of rows, since the block's shape fixes the order of the additions.
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                            bf16* __restrict__ out, const int* __restrict__ rows_index,
-                                                           int rows, int n, float eps) {
+                                                           int rows, int n, float eps, const float* __restrict__ w2,
+                                                           bf16* __restrict__ out2) {
   pdl_release_next();
   pdl_wait_prior();
   const int lane = threadIdx.x & 31, r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -171,6 +189,12 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
         __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * inv * g[u].x, v[u].y * inv * g[u].y);
         __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * inv * g[u].z, v[u].w * inv * g[u].w);
         o[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+        if (out2) {
+          const float4 g2 = ((const float4*)w2)[i];
+          lo = __floats2bfloat162_rn(v[u].x * inv * g2.x, v[u].y * inv * g2.y);
+          hi = __floats2bfloat162_rn(v[u].z * inv * g2.z, v[u].w * inv * g2.w);
+          ((uint2*)(out2 + (size_t)r * n))[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+        }
       }
     }
   }
@@ -184,11 +208,15 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
 template <int U>
 __global__ void __launch_bounds__(128) rmsnorm_rows_held_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                                 bf16* __restrict__ out, const int* __restrict__ rows_index,
-                                                                int rows, int n, float eps) {
-  extern __shared__ float4 weights[];   // [n / 4]
+                                                                int rows, int n, float eps, const float* __restrict__ w2,
+                                                                bf16* __restrict__ out2) {
+  extern __shared__ float4 weights[];   // [n / 4], and with a second norm its [n / 4] after them
   pdl_release_next();
   const int n4 = n / 4;
-  for (int i = threadIdx.x; i < n4; i += blockDim.x) weights[i] = ((const float4*)w)[i];
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    weights[i] = ((const float4*)w)[i];
+    if (out2) weights[n4 + i] = ((const float4*)w2)[i];
+  }
   pdl_wait_prior();
   const int lane = threadIdx.x & 31, r = min(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), rows - 1);
   const bool mine = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5) < rows;   // a warp beyond the rows only keeps the barrier
@@ -214,39 +242,54 @@ __global__ void __launch_bounds__(128) rmsnorm_rows_held_kernel(const float* __r
       __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * inv * g.x, v[u].y * inv * g.y);
       __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * inv * g.z, v[u].w * inv * g.w);
       o[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+      if (out2) {
+        const float4 g2 = weights[n4 + i];
+        lo = __floats2bfloat162_rn(v[u].x * inv * g2.x, v[u].y * inv * g2.y);
+        hi = __floats2bfloat162_rn(v[u].z * inv * g2.z, v[u].w * inv * g2.w);
+        ((uint2*)(out2 + (size_t)r * n))[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+      }
     }
   }
 }
 
 template <int U>
 static void launch_rows_held(const float* x, const float* w, bf16* out, const int* rows_index, int rows, int n, float eps,
-                             cudaStream_t stream) {
-  gb_launch(rmsnorm_rows_held_kernel<U>, (rows + 3) / 4, 128, (size_t)n * 4, stream, x, w, out, rows_index, rows, n, eps);
+                             const float* w2, bf16* out2, cudaStream_t stream) {
+  gb_launch(rmsnorm_rows_held_kernel<U>, (rows + 3) / 4, 128, (size_t)n * (out2 ? 8 : 4), stream, x, w, out, rows_index, rows, n,
+            eps, w2, out2);
+}
+
+// w2, out2: null, or a second norm of the same rows made in the same pass (same eps, same type of result).
+GB_EXPORT int gb_rmsnorm_pair(const float* x, const float* w, void* out, int out_dtype, const int* rows_index, int rows,
+                              int n, float eps, const float* w2, void* out2, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((w2 == nullptr) != (out2 == nullptr)) return GB_ERR_ARG;
+  const int threads = n >= 1024 ? 256 : 128;
+  const bool many = out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0;
+  if (out_dtype == GB_F32)
+    gb_launch(rmsnorm_kernel<float>, rows, threads, 0, stream, x, w, (float*)out, rows_index, n, eps, w2, (float*)out2);
+  else if (many && n <= 32 * 4 * 8)
+    launch_rows_held<8>(x, w, (bf16*)out, rows_index, rows, n, eps, w2, (bf16*)out2, stream);
+  else if (many && n <= 32 * 4 * 16)
+    launch_rows_held<16>(x, w, (bf16*)out, rows_index, rows, n, eps, w2, (bf16*)out2, stream);
+  else if (many && n <= 32 * 4 * 24)
+    launch_rows_held<24>(x, w, (bf16*)out, rows_index, rows, n, eps, w2, (bf16*)out2, stream);
+  else if (many && n <= 32 * 4 * 32)
+    launch_rows_held<32>(x, w, (bf16*)out, rows_index, rows, n, eps, w2, (bf16*)out2, stream);
+  else if (many && n <= 32 * 4 * 40)
+    launch_rows_held<40>(x, w, (bf16*)out, rows_index, rows, n, eps, w2, (bf16*)out2, stream);
+  else if (many)
+    gb_launch(rmsnorm_rows_kernel, (rows + 7) / 8, 256, 0, stream, x, w, (bf16*)out, rows_index, rows, n, eps, w2, (bf16*)out2);
+  else if (out_dtype == GB_BF16)
+    gb_launch(rmsnorm_kernel<bf16>, rows, threads, 0, stream, x, w, (bf16*)out, rows_index, n, eps, w2, (bf16*)out2);
+  else
+    return GB_ERR_DTYPE;
+  return gb_launch_status();
 }
 
 GB_EXPORT int gb_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows_index, int rows,
                          int n, float eps, cudaStream_t stream) {
-  if (rows <= 0) return 0;
-  const int threads = n >= 1024 ? 256 : 128;
-  if (out_dtype == GB_F32)
-    gb_launch(rmsnorm_kernel<float>, rows, threads, 0, stream, x, w, (float*)out, rows_index, n, eps);
-  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0 && n <= 32 * 4 * 8)
-    launch_rows_held<8>(x, w, (bf16*)out, rows_index, rows, n, eps, stream);
-  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0 && n <= 32 * 4 * 16)
-    launch_rows_held<16>(x, w, (bf16*)out, rows_index, rows, n, eps, stream);
-  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0 && n <= 32 * 4 * 24)
-    launch_rows_held<24>(x, w, (bf16*)out, rows_index, rows, n, eps, stream);
-  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0 && n <= 32 * 4 * 32)
-    launch_rows_held<32>(x, w, (bf16*)out, rows_index, rows, n, eps, stream);
-  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0 && n <= 32 * 4 * 40)
-    launch_rows_held<40>(x, w, (bf16*)out, rows_index, rows, n, eps, stream);
-  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0)
-    gb_launch(rmsnorm_rows_kernel, (rows + 7) / 8, 256, 0, stream, x, w, (bf16*)out, rows_index, rows, n, eps);
-  else if (out_dtype == GB_BF16)
-    gb_launch(rmsnorm_kernel<bf16>, rows, threads, 0, stream, x, w, (bf16*)out, rows_index, n, eps);
-  else
-    return GB_ERR_DTYPE;
-  return gb_launch_status();
+  return gb_rmsnorm_pair(x, w, out, out_dtype, rows_index, rows, n, eps, nullptr, nullptr, stream);
 }
 
 // ------------------------------------------------------------------ per-head norm + rotation + cache write

@@ -190,8 +190,10 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, s
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
-            rows_index: Optional[torch.Tensor] = None):
-    """out[r] = rmsnorm(x[rows_index[r] or r]) * weight.  x float32 [*, n]; weight float32 [n]."""
+            rows_index: Optional[torch.Tensor] = None, second=None):
+    """out[r] = rmsnorm(x[rows_index[r] or r]) * weight.  x float32 [*, n]; weight float32 [n].
+    ``second`` (weight2, out2): another norm of the same rows with the same eps, whose statistics are
+    the same; out2[r] = rmsnorm(x[...]) * weight2 is written in the same pass."""
     _cuda(x, weight, out, rows_index)
     assert x.dtype == torch.float32 and weight.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
     n = x.shape[-1]
@@ -199,10 +201,15 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
     assert weight.numel() == n and out.shape[-1] == n
     if rows_index is not None:
         assert rows_index.dtype == torch.int32 and rows_index.numel() == rows
-    f = _fn("elementwise", "gb_rmsnorm",
-            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
+    w2, out2 = second if second is not None else (None, None)
+    if second is not None:
+        _cuda(w2, out2)
+        assert w2.dtype == torch.float32 and w2.numel() == n and out2.shape == out.shape and out2.dtype == out.dtype
+        assert out2.is_contiguous()
+    f = _fn("elementwise", "gb_rmsnorm_pair",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p])
     _check(f(x.data_ptr(), weight.data_ptr(), out.data_ptr(), dtype_code(out.dtype), _ptr(rows_index), rows, n,
-             eps, _stream()), "rmsnorm", "norm", _nbytes(out, weight) + rows * n * 4)
+             eps, _ptr(w2), _ptr(out2), _stream()), "rmsnorm", "norm", _nbytes(out, weight, out2, w2) + rows * n * 4)
 
 
 def head_norm_rope_cache(qkv, nh, nkv, hd, rot, q_weight, k_weight, eps, inv_freq, q_scale, tok_pos, tok_seq,

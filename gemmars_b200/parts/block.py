@@ -77,8 +77,12 @@ class ParallelBlock(Block):
 
     def forward(self, ctx, x, caches, writes_cache=True):
         mine = self.split_caches(caches)
-        h = self.norm.forward(ctx, x)        # read by both branches before either changes x
-        h_ffn = self.ffn_norm.forward(ctx, x) if self.ffn_norm is not None else h
+        # read by both branches before either changes x; two norms of the same x are one pass where they can be
+        if self.ffn_norm is not None and hasattr(self.norm, "forward_with"):
+            h, h_ffn = self.norm.forward_with(ctx, x, self.ffn_norm)
+        else:
+            h = self.norm.forward(ctx, x)
+            h_ffn = self.ffn_norm.forward(ctx, x) if self.ffn_norm is not None else h
         self.mixer.forward(ctx, h, x, mine["mixer"], writes_cache)
         if self.ffn is not None:
             self.ffn.forward(ctx, h_ffn, x)

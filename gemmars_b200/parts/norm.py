@@ -5,7 +5,9 @@ src/config.rs:465-469).  Input: rows of the float32 residual stream; output: act
 ``offset`` (default 0): the stored weight is a deviation from it, w = offset + stored (a
 checkpoint that keeps its norm weights around zero has offset 1); the sum is taken once, in
 float32, when the weight is loaded.  ``add_normed`` is the norm on the other side of a sublayer:
-it norms the sublayer's float32 output and adds it into the residual stream."""
+it norms the sublayer's float32 output and adds it into the residual stream.  ``forward_with`` is two
+norms of the same rows in one pass (a block whose mixer and feed-forward each read a norm of their
+own of the same x)."""
 from __future__ import annotations
 
 import torch
@@ -46,6 +48,16 @@ class RMSNorm(Part):
         out = torch.empty((rows, self.size), dtype=self.act_dtype, device=x.device)
         kernels.rmsnorm(x, self.weight, out, self.eps, rows_index)
         return out
+
+    def forward_with(self, ctx, x, other: "RMSNorm"):
+        """(this norm of x, ``other``'s norm of x) in one pass: two norms of the same rows with the same
+        size and eps share their statistics and differ in their weights alone."""
+        if not isinstance(other, RMSNorm) or other.size != self.size or other.eps != self.eps or other.act_dtype != self.act_dtype:
+            return self.forward(ctx, x), other.forward(ctx, x)
+        out = torch.empty((x.shape[0], self.size), dtype=self.act_dtype, device=x.device)
+        out2 = torch.empty_like(out)
+        kernels.rmsnorm(x, self.weight, out, self.eps, second=(other.weight, out2))
+        return out, out2
 
     def add_normed(self, ctx, y, x, then=None):
         """x += norm(y): ``y`` a sublayer's float32 output, ``x`` the residual stream.  ``then``: an

@@ -91,6 +91,25 @@ def test_second_half_of_a_two_matrix_projection(mode, w_dtype, tokens, groups, g
     assert got.shape == want.shape and np.abs(got - want).max() < 3e-6 * max(1.0, np.abs(want).max())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,n", [(1, 72), (9, 52), (8, 4096), (600, 320), (513, 1024), (700, 5120), (520, 6000), (3, 6001)])
+def test_two_norms_of_the_same_rows_in_one_pass(dtype, rows, n):
+    """Every form of the norm kernel (few rows, many rows held in registers, rows too wide for that,
+    widths that are no multiple of four): the pair gives the bits of two norms run one after the other."""
+    from gemmars_b200 import kernels
+    rng = np.random.default_rng(rows + n)
+    x, xn = _rand(rng, (rows, n), scale=3.0)
+    w1, w1n = _rand(rng, (n,), shift=1.0, scale=0.2)
+    w2, w2n = _rand(rng, (n,), shift=-0.5, scale=0.7)
+    outs = [torch.empty((rows, n), dtype=_dt(dtype), device=DEV) for _ in range(4)]
+    kernels.rmsnorm(x, w1, outs[0], 1e-5)
+    kernels.rmsnorm(x, w2, outs[1], 1e-5)
+    kernels.rmsnorm(x, w1, outs[2], 1e-5, second=(w2, outs[3]))
+    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])
+    want = plain.rms_norm(xn, w2n, 1e-5)
+    assert np.abs(outs[3].double().cpu().numpy() - want).max() < (1e-5 if dtype == "float32" else 1e-2) * np.abs(want).max()
+
+
 def _scan_case(rng, lens, heads, groups, dim, vdim, planted):
     """Random q | k | v rows (one tensor), beta logits and decays per sequence.  With ``planted``, in
     the longest sequence one early key is made loud on channels whose decay is held at one, with a
