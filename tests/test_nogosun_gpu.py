@@ -554,6 +554,98 @@ def test_routed_layers_of_unequal_shapes_in_long_prompts(tmp_path_factory):
         assert np.abs(got - want).max() <= 2 * TOL_BF16 * np.abs(want).max(), f"a prompt of {n} tokens"
 
 
+def _random_configuration(rng):
+    """Layers of the three kinds in any order with sizes drawn at random, some of them running the
+    tensors of another layer, named before or after them."""
+    def moe():
+        if rng.random() < 0.15:
+            return None
+        experts = int(rng.integers(1, 13))
+        return _nogosun_moe(experts, int(rng.integers(1, min(experts, 5) + 1)), int(rng.choice([24, 32, 40, 64])))
+
+    def attention():
+        g = int(rng.choice([1, 2, 4]))
+        d = int(rng.choice([16, 24, 32, 40, 64, 80]))
+        size = int(rng.integers(3, 150)) if rng.random() < 0.85 else None
+        keep = int(rng.choice([0, 1, 5, 66])) if size is not None and rng.random() < 0.8 else None
+        dims = int(rng.choice([0, d, d // 2 - (d // 2) % 2, 4]))
+        scaling = None if rng.random() < 0.4 else (float(rng.choice([2.0, 6.0, 20.0])), int(rng.choice([32, 300, 2000])),
+                                                   float(rng.choice([16.0, 4.0])), float(rng.choice([2.0, 0.5])))
+        return _nogosun_attention(g * int(rng.choice([1, 2, 3])), g, d, float(d ** -0.5 * rng.uniform(0.7, 1.5)), size, keep,
+                                  float(rng.choice([1e4, 3e5, 400.0])), dims if dims else None, scaling if dims else None)
+
+    def delta():
+        g = int(rng.choice([1, 2, 3]))
+        d = int(rng.choice([16, 24, 32, 48, 64, 72]))
+        return _nogosun_delta(g * int(rng.choice([1, 2])), g, d, int(rng.choice([16, 24, 40, 64, d])), int(rng.integers(1, 6)),
+                              int(rng.choice([3, 8, 20])), int(rng.choice([2, 8, 12])))
+
+    def pair():
+        g = int(rng.choice([1, 2]))
+        d = int(rng.choice([16, 24, 32, 64]))
+        left = (g * int(rng.choice([1, 2, 4])), g, d, int(rng.choice([16, 40, 64, d])), float(d ** -0.5),
+                float(rng.choice([4.0, 20.0])) if rng.random() < 0.8 else None,
+                (float(rng.uniform(0.1, 1.0)), int(rng.choice([1, 9, 64]))) if rng.random() < 0.8 else None)
+        right = (int(rng.integers(1, 6)), int(rng.choice([16, 24, 48, 64])), int(rng.choice([16, 40, 64])),
+                 float(rng.choice([1.0, 3.0, 12.0])), int(rng.choice([3, 8, 10])))
+        return _nogosun_pair(left, right, float(rng.uniform(0.3, 1.2)), float(rng.uniform(0.3, 1.2)))
+
+    layers = []
+    for i in range(int(rng.integers(3, 8))):
+        owners = [j for j, layer in enumerate(layers) if "weights_of" not in layer]
+        if owners and rng.random() < 0.3:
+            j = int(rng.choice(owners))
+            layers.append(dict(json.loads(json.dumps(layers[j])), weights_of=j))
+            continue
+        kind = str(rng.choice(["attention", "channel_delta", "parallel"]))
+        layers.append({"type": kind, "mixer": {"attention": attention, "channel_delta": delta, "parallel": pair}[kind](),
+                       "mlp": moe()})
+    sharers = [i for i, layer in enumerate(layers) if "weights_of" in layer]
+    if sharers and rng.random() < 0.5:            # the later layer owns the tensors, the earlier one names it
+        i = sharers[0]
+        j = layers[i].pop("weights_of")
+        if not any(layer.get("weights_of") == j for layer in layers):
+            layers[j]["weights_of"] = i
+        else:
+            layers[i]["weights_of"] = j
+    return {"architecture": "Nogosun", "vocab": int(rng.choice([97, 300, 1000])), "width": int(rng.choice([52, 64, 96, 136, 200])),
+            "embedding": {"scale": float(rng.uniform(1.0, 20.0))}, "norm": {"eps": float(rng.choice([1e-5, 1e-6]))},
+            "layers": layers}
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
+def test_random_configurations(seed, tmp_path_factory):
+    """A configuration drawn at random, in float32: three unequal prompts in one batch, then token by
+    token together until the shortest ends and on, against the plain implementation's whole prompts."""
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    rng = np.random.default_rng(1000 + seed)
+    raw = _random_configuration(rng)
+    folder = _sharp_folder(tmp_path_factory, raw, seed=seed, factor=2.0)
+    cfg, w = plain.load_folder(folder)
+    lens = [int(n) for n in rng.choice([2, 17, 70, 131, 200], 3)]
+    reqs = [rng.integers(0, raw["vocab"], n).tolist() for n in lens]
+    ref = [plain.forward(cfg, w, r) for r in reqs]
+    scale = max(float(np.abs(r).max()) for r in ref)
+    runner = Runner(build_model(folder, dtype="float32"), max_tokens=12 * PAGE, max_batch=3)
+    slots = [runner.open() for _ in reqs]
+    heads = [max(1, n - 9) for n in lens]
+    errs = []
+    out = runner.step([StepItem(s, r[:h], range(h)) for s, r, h in zip(slots, reqs, heads)]).cpu().numpy()
+    at = 0
+    for r, h in zip(ref, heads):
+        errs += list(np.abs(out[at:at + h] - r[:h]).max(axis=1))
+        at += h
+    for k in range(9):
+        live = [i for i in range(3) if heads[i] + k < lens[i]]
+        out = runner.step([StepItem(slots[i], [reqs[i][heads[i] + k]], [0]) for i in live]).cpu().numpy()
+        errs += [np.abs(out[n] - ref[i][heads[i] + k]).max() for n, i in enumerate(live)]
+    assert len(errs) == sum(lens)
+    assert max(errs) <= TOL_F32 * scale, f"{max(errs) / scale:.2e} of the largest logit, configuration {json.dumps(raw)}"
+    for s in slots:
+        runner.close(s)
+    assert runner.cache.pages_held() == 0
+
+
 def test_greedy_generation_through_the_engine(models):
     from gemmars_b200 import Engine
     folder, cfg, w, reqs, _ = models["A"]
